@@ -1,0 +1,109 @@
+/*
+ * sk_w2a8.h — C ABI of the B200 (sm_100a) W2A8 GEMM: 2-bit packed weights x int8 activations.
+ *
+ *   out[m, n] = cast( x_scale[m] * sum_g  w_scale[g, n] * fp32( sum_{k in group g} x_q[m, k] * (code[n, k] - zero_point) ) )
+ *
+ * Operand format (device memory, caller-owned, row-major):
+ *   x_q      int8   [M, K]      leading dimension ld_x (elements = bytes), ld_x % 16 == 0, 16-byte aligned
+ *   x_scale  float  [M]
+ *   w_packed uint8  [N, K/4]    byte j of row n holds codes k = 4j..4j+3, k = 4j in bits 7:6
+ *                               (the layout produced by the reference's matrix_packer.py:29-34)
+ *   w_scale  half   [K/G, N]    per-group scales, groups along K (orientation of quantization.py:23-38)
+ *   out      half | bfloat16 [M, N]  leading dimension ld_out >= N (elements)
+ * Constraints: K % 32 == 0, K % G == 0, G % 32 == 0 and (G % 128 == 0 or 128 % G == 0).
+ *
+ * The reference has no FFI for this path; the entry points below take the place of its C++ host
+ * launcher  gemm_tn(m, n, a_k, b_k, alpha, A, ldA, B, ldB, beta, C, ldC, stream)
+ * (slimkernels/cute/gemm/wgmma_sm90_W2A8.cu:428-437) and keep its conventions: raw device pointers,
+ * caller-owned buffers, leading dimensions in elements, output written in place.  Unlike that launcher
+ * the stream argument is honoured, errors are returned (no abort, no prints) and results are stored.
+ *
+ * All functions return 0 (SK_OK) or a negative sk_status.  No exceptions cross this boundary.
+ * Calls on one plan must be externally ordered; a plan is bound to one device.
+ */
+#ifndef SK_W2A8_H_
+#define SK_W2A8_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct sk_w2a8_plan sk_w2a8_plan;
+typedef void* sk_stream_t; /* cudaStream_t */
+
+typedef enum sk_status {
+  SK_OK = 0,
+  SK_ERR_NULL_POINTER = -1,
+  SK_ERR_BAD_SHAPE = -2,
+  SK_ERR_BAD_ALIGNMENT = -3,
+  SK_ERR_UNSUPPORTED_ARCH = -4, /* device is not compute capability 10.x */
+  SK_ERR_CUDA = -5,             /* a CUDA runtime/driver call failed; see sk_w2a8_last_cuda_error */
+  SK_ERR_DEVICE_TIMEOUT = -6,   /* a bounded wait inside a kernel expired; see sk_w2a8_last_device_status */
+  SK_ERR_BAD_ARGUMENT = -7,
+  SK_ERR_OUT_OF_MEMORY = -8,
+  SK_ERR_UNAVAILABLE = -9       /* requested kernel/option not available for this plan */
+} sk_status;
+
+typedef enum sk_out_dtype { SK_OUT_F16 = 0, SK_OUT_BF16 = 1 } sk_out_dtype;
+
+/* Layout of the weight bytes handed to sk_w2a8_plan_create. */
+typedef enum sk_weight_layout {
+  SK_WEIGHT_ROWMAJOR = 0, /* matrix_packer.py layout, uint8 [N, K/4]; the plan makes its own tiled copy */
+  SK_WEIGHT_TILED = 1     /* output of sk_w2a8_repack; borrowed, must outlive the plan */
+} sk_weight_layout;
+
+/* Keys of sk_w2a8_set_option (testing / tuning; 0 or SK_AUTO restores the heuristic). */
+typedef enum sk_option {
+  SK_OPT_KERNEL = 1,      /* 0 auto, 1 tcgen05 kernel, 2 CUDA-core checker kernel (needs SK_WEIGHT_ROWMAJOR) */
+  SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 */
+  SK_OPT_SPLIT_K = 3      /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
+} sk_option;
+
+/* -------- weight preparation ("Blackwell tile order") ------------------------------------------
+ * The tcgen05 kernel streams weights in a tiled order: 128 output rows x 128 K-codes per 4 KiB block,
+ * blocks of one 128-row tile contiguous along K, bit order inside each 32-bit word chosen so that 16
+ * codes expand to 16 int8 bytes with four shift+mask pairs.  The repack is a pure permutation of the
+ * 2-bit codes (plus zero padding of N to 128 and K to 128); sk_w2a8_unrepack inverts it exactly.
+ * Replaces nothing in the reference; anticipated there by its pre-tiled copy test
+ * (slimkernels/cute/gemm/test_bc.cu:70-74). */
+int64_t sk_w2a8_tiled_bytes(int64_t N, int64_t K);
+int sk_w2a8_repack(const uint8_t* w_packed, int64_t N, int64_t K, uint8_t* w_tiled, sk_stream_t stream);
+int sk_w2a8_unrepack(const uint8_t* w_tiled, int64_t N, int64_t K, uint8_t* w_packed, sk_stream_t stream);
+
+/* -------- plan ------------------------------------------------------------------------------------
+ * Binds one weight matrix to a device: validates shapes/alignment, builds the tiled weight copy (or
+ * borrows one), allocates a 4-byte device status word.  Stands where gemm_tn builds its tilers, smem
+ * layouts and tensor maps on every call (wgmma_sm90_W2A8.cu:448-466).  Synchronises `device` once. */
+int sk_w2a8_plan_create(sk_w2a8_plan** plan, int device, int64_t N, int64_t K, int group_size,
+                        int zero_point, const uint8_t* w, int w_layout, const void* w_scale_f16,
+                        int out_dtype);
+int sk_w2a8_plan_destroy(sk_w2a8_plan* plan);
+int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value);
+
+/* -------- the GEMM (replaces gemm_tn, wgmma_sm90_W2A8.cu:428-506) ---------------------------------
+ * Stream-ordered and asynchronous; no allocation, no synchronisation. */
+int sk_w2a8_gemm(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
+                 void* out, int64_t ld_out, sk_stream_t stream);
+
+/* Same contraction, but stores the exact per-group integer partial sums
+ * partials[g, m, n] (int32, [K/G, M, N] contiguous) instead of the scaled output. */
+int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,
+                                int32_t* partials, sk_stream_t stream);
+
+/* -------- diagnostics -----------------------------------------------------------------------------*/
+/* Synchronously reads (and clears) the plan's device status word: 0, or a code naming the wait that
+ * expired inside the kernel (role * 16 + barrier kind).  Non-zero maps to SK_ERR_DEVICE_TIMEOUT. */
+int sk_w2a8_last_device_status(sk_w2a8_plan* plan, int* device_status);
+int sk_w2a8_last_cuda_error(const sk_w2a8_plan* plan);
+/* Describes the launch the plan would make for M tokens: token tile, split-K factor, CTAs, kernel kind. */
+int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* split_k, int* ctas,
+                         int* kernel_kind);
+const char* sk_status_string(int status);
+int sk_w2a8_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SK_W2A8_H_ */

@@ -1,0 +1,536 @@
+// C ABI of the W2A8 GEMM (declared in include/sk_w2a8.h) plus the small kernels around the main one:
+// weight repack / unrepack, and a CUDA-core checker kernel that reads the reference byte layout directly.
+#include "../../include/sk_w2a8.h"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "w2a8_umma.cuh"
+
+namespace sk {
+
+// ------------------------------------------------------------------------------------------------
+// Tiled weight order.  Block (tile T, k-block B) is 4096 bytes at ((T * k_blocks + B) * 4096); inside it the
+// 32-bit word for (row r, 16-code chunk c) sits at byte (c / 4) * 2048 + r * 16 + (c % 4) * 4 and holds
+//   sum_{j=0..3} sum_{b=0..3} code[n = 128 T + r][k = 128 B + 16 c + 4 j + b] << (8 b + 2 j).
+// The source byte for codes 4j..4j+3 of that chunk (matrix_packer order: first code in bits 7:6) is
+// w_packed[n][(128 B + 16 c) / 4 + j].
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t tiled_word_from_bytes(const uint8_t (&src)[4]) {
+  uint32_t w = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t code = (src[j] >> (6 - 2 * b)) & 3u;
+      w |= code << (8 * b + 2 * j);
+    }
+  }
+  return w;
+}
+
+__global__ void repack_kernel(const uint8_t* __restrict__ w_packed, uint32_t* __restrict__ w_tiled, long long N,
+                              long long K, int k_blocks, long long total_words) {
+  const long long row_bytes = K / 4;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total_words;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    // idx enumerates destination words in memory order
+    const long long block = idx >> 10;             // 1024 words per 4 KiB block
+    const int in_block = static_cast<int>(idx & 1023);
+    const int half = in_block >> 9;                // 512 words per half
+    const int r = (in_block >> 2) & 127;
+    const int c = half * 4 + (in_block & 3);
+    const long long T = block / k_blocks, B = block % k_blocks;
+    const long long n = T * 128 + r;
+    const long long k = B * 128 + 16 * c;
+    uint8_t src[4] = {0, 0, 0, 0};
+    if (n < N) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (k + 4 * j < K) src[j] = w_packed[n * row_bytes + k / 4 + j];
+    }
+    w_tiled[idx] = tiled_word_from_bytes(src);
+  }
+}
+
+__global__ void unrepack_kernel(const uint32_t* __restrict__ w_tiled, uint8_t* __restrict__ w_packed, long long N,
+                                long long K, int k_blocks, long long total_words) {
+  const long long row_bytes = K / 4;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total_words;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long block = idx >> 10;
+    const int in_block = static_cast<int>(idx & 1023);
+    const int half = in_block >> 9;
+    const int r = (in_block >> 2) & 127;
+    const int c = half * 4 + (in_block & 3);
+    const long long T = block / k_blocks, B = block % k_blocks;
+    const long long n = T * 128 + r;
+    const long long k = B * 128 + 16 * c;
+    if (n >= N) continue;
+    const uint32_t w = w_tiled[idx];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (k + 4 * j >= K) continue;
+      uint32_t byte = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) byte |= ((w >> (8 * b + 2 * j)) & 3u) << (6 - 2 * b);
+      w_packed[n * row_bytes + k / 4 + j] = static_cast<uint8_t>(byte);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CUDA-core checker kernel.  Reads the reference byte layout (uint8 [N, K/4], first code in bits 7:6)
+// directly, so it does not depend on the repack, the tensor-core path or TMA.  One thread per output
+// (m, n): 32 consecutive n per warp (x loads are warp-uniform), exact int32 group partials via dp4a,
+// fp32 scaling in group order.  Used to cross-check the tcgen05 kernel at sizes the CPU oracle cannot reach.
+// ------------------------------------------------------------------------------------------------
+__global__ void w2a8_simt_kernel(const int8_t* __restrict__ x_q, long long ld_x, const float* __restrict__ x_scale,
+                                 const uint8_t* __restrict__ w_packed, const __half* __restrict__ w_scale,
+                                 void* __restrict__ out, long long ld_out, int32_t* __restrict__ partials, int M, int N,
+                                 int K, int G, int zero_point, int out_bf16) {
+  const int n = blockIdx.x * 32 + threadIdx.x;
+  const int m = blockIdx.y * blockDim.y + threadIdx.y;
+  if (n >= N || m >= M) return;
+  const uint8_t* wrow = w_packed + static_cast<size_t>(n) * (K / 4);
+  const int8_t* xrow = x_q + static_cast<size_t>(m) * ld_x;
+  const int groups = K / G;
+  float acc = 0.f;
+  for (int g = 0; g < groups; ++g) {
+    int32_t part = 0;
+    for (int k = g * G; k < (g + 1) * G; k += 4) {
+      const uint32_t b = wrow[k >> 2];
+      const int c0 = static_cast<int>((b >> 6) & 3u) - zero_point, c1 = static_cast<int>((b >> 4) & 3u) - zero_point;
+      const int c2 = static_cast<int>((b >> 2) & 3u) - zero_point, c3 = static_cast<int>(b & 3u) - zero_point;
+      const uint32_t wv = (static_cast<uint32_t>(c0) & 0xffu) | ((static_cast<uint32_t>(c1) & 0xffu) << 8) |
+                          ((static_cast<uint32_t>(c2) & 0xffu) << 16) | ((static_cast<uint32_t>(c3) & 0xffu) << 24);
+      const int xv = *reinterpret_cast<const int*>(xrow + k);
+      part = __dp4a(xv, static_cast<int>(wv), part);
+    }
+    if (partials) partials[(static_cast<size_t>(g) * M + m) * N + n] = part;
+    acc = fmaf(__half2float(w_scale[static_cast<size_t>(g) * N + n]), static_cast<float>(part), acc);
+  }
+  if (out) {
+    const float y = acc * x_scale[m];
+    uint16_t* o = reinterpret_cast<uint16_t*>(out) + static_cast<size_t>(m) * ld_out + n;
+    *o = out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y)) : __half_as_ushort(__float2half_rn(y));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct CachedMap {
+  const void* ptr;
+  long long M, ld;
+  int block_m;
+  CUtensorMap map;
+};
+
+}  // namespace sk
+
+struct sk_w2a8_plan {
+  int device = 0;
+  long long N = 0, K = 0;
+  int G = 128, zero_point = 1, out_dtype = SK_OUT_F16;
+  int k_blocks = 0, n_tiles = 0, sm_count = 148;
+  const uint8_t* w_rowmajor = nullptr;  // borrowed (may be null when created from a tiled buffer)
+  const uint8_t* w_tiled = nullptr;     // owned or borrowed
+  uint8_t* w_tiled_owned = nullptr;
+  const __half* w_scale = nullptr;      // borrowed
+  int* status = nullptr;                // device, owned
+  int last_cuda_error = 0;
+  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0;
+  std::vector<sk::CachedMap> maps;      // small cache of activation tensor maps
+  std::mutex mu;
+};
+
+namespace sk {
+
+static int cuda_fail(sk_w2a8_plan* plan, cudaError_t e) {
+  if (plan) plan->last_cuda_error = static_cast<int>(e);
+  (void)cudaGetLastError();
+  return e == cudaErrorMemoryAllocation ? SK_ERR_OUT_OF_MEMORY : SK_ERR_CUDA;
+}
+
+struct LaunchChoice {
+  int kernel;      // 1 tcgen05, 2 CUDA-core checker
+  int token_tile;  // 16 / 32 / 64 / 128
+  int split_k;     // 1 / 2 / 4 / 8
+};
+
+static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
+  LaunchChoice c;
+  c.kernel = plan->opt_kernel ? plan->opt_kernel : 1;
+  if (plan->opt_token_tile) c.token_tile = plan->opt_token_tile;
+  else c.token_tile = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  const int groups = static_cast<int>(plan->K / plan->G);
+  if (plan->opt_split_k) c.split_k = plan->opt_split_k;
+  else {
+    // Fill the machine: split the K range of a tile over a cluster while there are fewer tiles than ~2 per SM.
+    const long long tiles = plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile);
+    int s = 1;
+    if (c.token_tile <= 64)
+      while (s < 8 && tiles * s < 2LL * plan->sm_count && groups / (2 * s) >= 2) s *= 2;
+    c.split_k = s;
+  }
+  if (c.split_k > groups) c.split_k = 1;
+  if (c.token_tile > 64) c.split_k = 1;   // the cluster reduction buffer is sized for small token tiles
+  return c;
+}
+
+template <int BLOCK_M, int LSTAGES, int ESTAGES, bool DUMP>
+static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
+                       cudaStream_t stream) {
+  using L = SmemLayout<BLOCK_M, LSTAGES, ESTAGES>;
+  auto kern = w2a8_umma_kernel<BLOCK_M, LSTAGES, ESTAGES, DUMP>;
+  static int configured_device_mask[64] = {0};
+  if (plan->device < 64 && !configured_device_mask[plan->device]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    if (e != cudaSuccess) return cuda_fail(plan, e);
+    configured_device_mask[plan->device] = 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan->n_tiles, m_tiles, split_k);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kDynamicBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (split_k > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = split_k;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, prm);
+  if (e != cudaSuccess) return cuda_fail(plan, e);
+  return SK_OK;
+}
+
+template <bool DUMP>
+static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const GemmParams& prm,
+                         int m_tiles, int split_k, cudaStream_t stream) {
+  switch (token_tile) {
+    case 16: return launch_umma<16, 8, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 32: return launch_umma<32, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 64: return launch_umma<64, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 128: return launch_umma<128, 4, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    default: return SK_ERR_BAD_ARGUMENT;
+  }
+}
+
+static int get_x_map(sk_w2a8_plan* plan, const int8_t* x_q, long long M, long long ld_x, int block_m,
+                     CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(plan->mu);
+  for (const auto& c : plan->maps)
+    if (c.ptr == x_q && c.M == M && c.ld == ld_x && c.block_m == block_m) { *out = c.map; return SK_OK; }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return SK_ERR_CUDA;
+  CachedMap cm;
+  cm.ptr = x_q; cm.M = M; cm.ld = ld_x; cm.block_m = block_m;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(plan->K), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_x)};
+  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(block_m)};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(&cm.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(x_q), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { plan->last_cuda_error = static_cast<int>(r); return SK_ERR_CUDA; }
+  if (plan->maps.size() >= 16) plan->maps.erase(plan->maps.begin());
+  plan->maps.push_back(cm);
+  *out = cm.map;
+  return SK_OK;
+}
+
+static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long long ld_x, const float* x_scale,
+                    void* out, long long ld_out, int32_t* partials, cudaStream_t stream) {
+  if (!plan || !x_q) return SK_ERR_NULL_POINTER;
+  if (!partials && (!x_scale || !out)) return SK_ERR_NULL_POINTER;
+  if (M <= 0 || M > 0x7fffffffLL / 2) return SK_ERR_BAD_SHAPE;
+  if (ld_x < plan->K) return SK_ERR_BAD_SHAPE;
+  if (!partials && ld_out < plan->N) return SK_ERR_BAD_SHAPE;
+  if ((ld_x % 16) != 0 || (reinterpret_cast<uintptr_t>(x_q) & 15) != 0) return SK_ERR_BAD_ALIGNMENT;
+  if (out && (reinterpret_cast<uintptr_t>(out) & 1) != 0) return SK_ERR_BAD_ALIGNMENT;
+
+  int cur = -1;
+  cudaError_t e = cudaGetDevice(&cur);
+  if (e != cudaSuccess) return cuda_fail(plan, e);
+  if (cur != plan->device) {
+    e = cudaSetDevice(plan->device);
+    if (e != cudaSuccess) return cuda_fail(plan, e);
+  }
+  LaunchChoice ch = choose(plan, M);
+  if (partials) ch.split_k = 1;
+  int rc = SK_OK;
+  if (ch.kernel == 2) {
+    if (!plan->w_rowmajor) rc = SK_ERR_UNAVAILABLE;
+    else {
+      dim3 block(32, 8, 1);
+      dim3 grid(static_cast<unsigned>((plan->N + 31) / 32), static_cast<unsigned>((M + 7) / 8), 1);
+      w2a8_simt_kernel<<<grid, block, 0, stream>>>(x_q, ld_x, x_scale, plan->w_rowmajor, plan->w_scale, out, ld_out,
+                                                   partials, static_cast<int>(M), static_cast<int>(plan->N),
+                                                   static_cast<int>(plan->K), plan->G, plan->zero_point,
+                                                   plan->out_dtype == SK_OUT_BF16);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) rc = cuda_fail(plan, e);
+    }
+  } else {
+    CUtensorMap map;
+    rc = get_x_map(plan, x_q, M, ld_x, ch.token_tile, &map);
+    if (rc == SK_OK) {
+      GemmParams prm;
+      prm.w_tiled = plan->w_tiled;
+      prm.w_scale = plan->w_scale;
+      prm.x_scale = x_scale;
+      prm.out = out;
+      prm.partials = partials;
+      prm.status = plan->status;
+      prm.ld_out = ld_out;
+      prm.M = static_cast<int>(M);
+      prm.N = static_cast<int>(plan->N);
+      prm.K = static_cast<int>(plan->K);
+      prm.k_blocks = plan->k_blocks;
+      prm.k_steps = static_cast<int>(plan->K / 32);
+      prm.steps_per_group = plan->G / 32;
+      prm.groups = static_cast<int>(plan->K / plan->G);
+      prm.zero_point = plan->zero_point;
+      prm.out_bf16 = plan->out_dtype == SK_OUT_BF16;
+      const int m_tiles = static_cast<int>((M + ch.token_tile - 1) / ch.token_tile);
+      if (m_tiles > 65535) rc = SK_ERR_BAD_SHAPE;
+      else if (partials) rc = dispatch_umma<true>(plan, ch.token_tile, map, prm, m_tiles, 1, stream);
+      else rc = dispatch_umma<false>(plan, ch.token_tile, map, prm, m_tiles, ch.split_k, stream);
+    }
+  }
+  if (cur != plan->device) (void)cudaSetDevice(cur);
+  return rc;
+}
+
+static int repack_common(bool forward, const uint8_t* src, long long N, long long K, uint8_t* dst,
+                         cudaStream_t stream) {
+  if (!src || !dst) return SK_ERR_NULL_POINTER;
+  if (N <= 0 || K <= 0 || (K % 32) != 0) return SK_ERR_BAD_SHAPE;
+  const uint8_t* tiled = forward ? dst : src;
+  if ((reinterpret_cast<uintptr_t>(tiled) & 15) != 0) return SK_ERR_BAD_ALIGNMENT;
+  const int k_blocks = static_cast<int>((K + 127) / 128);
+  const long long n_tiles = (N + 127) / 128;
+  const long long total_words = n_tiles * k_blocks * 1024;
+  const int threads = 256;
+  const long long want = (total_words + threads - 1) / threads;
+  const int blocks = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+  if (forward)
+    repack_kernel<<<blocks, threads, 0, stream>>>(src, reinterpret_cast<uint32_t*>(dst), N, K, k_blocks, total_words);
+  else
+    unrepack_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const uint32_t*>(src), dst, N, K, k_blocks,
+                                                    total_words);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return SK_ERR_CUDA;
+  return SK_OK;
+}
+
+}  // namespace sk
+
+// ================================================================================================
+// extern "C"
+// ================================================================================================
+extern "C" {
+
+int sk_w2a8_version(void) { return 100; }
+
+const char* sk_status_string(int status) {
+  switch (status) {
+    case SK_OK: return "ok";
+    case SK_ERR_NULL_POINTER: return "null pointer";
+    case SK_ERR_BAD_SHAPE: return "bad shape";
+    case SK_ERR_BAD_ALIGNMENT: return "bad alignment";
+    case SK_ERR_UNSUPPORTED_ARCH: return "unsupported architecture (needs compute capability 10.x)";
+    case SK_ERR_CUDA: return "CUDA error";
+    case SK_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
+    case SK_ERR_BAD_ARGUMENT: return "bad argument";
+    case SK_ERR_OUT_OF_MEMORY: return "out of device memory";
+    case SK_ERR_UNAVAILABLE: return "not available for this plan";
+    default: return "unknown status";
+  }
+}
+
+int64_t sk_w2a8_tiled_bytes(int64_t N, int64_t K) {
+  if (N <= 0 || K <= 0) return 0;
+  return ((N + 127) / 128) * ((K + 127) / 128) * 4096;
+}
+
+int sk_w2a8_repack(const uint8_t* w_packed, int64_t N, int64_t K, uint8_t* w_tiled, sk_stream_t stream) {
+  return sk::repack_common(true, w_packed, N, K, w_tiled, static_cast<cudaStream_t>(stream));
+}
+
+int sk_w2a8_unrepack(const uint8_t* w_tiled, int64_t N, int64_t K, uint8_t* w_packed, sk_stream_t stream) {
+  return sk::repack_common(false, w_tiled, N, K, w_packed, static_cast<cudaStream_t>(stream));
+}
+
+int sk_w2a8_plan_create(sk_w2a8_plan** out, int device, int64_t N, int64_t K, int group_size, int zero_point,
+                        const uint8_t* w, int w_layout, const void* w_scale_f16, int out_dtype) {
+  if (!out) return SK_ERR_NULL_POINTER;
+  *out = nullptr;
+  if (!w || !w_scale_f16) return SK_ERR_NULL_POINTER;
+  if (N <= 0 || K <= 0 || N > (1LL << 30) || K > (1LL << 30)) return SK_ERR_BAD_SHAPE;
+  if (group_size <= 0 || (group_size % 32) != 0 || (K % group_size) != 0 || (K % 32) != 0) return SK_ERR_BAD_SHAPE;
+  if (!((group_size % 128) == 0 || (128 % group_size) == 0)) return SK_ERR_BAD_SHAPE;
+  if (zero_point < 0 || zero_point > 3) return SK_ERR_BAD_ARGUMENT;
+  if (out_dtype != SK_OUT_F16 && out_dtype != SK_OUT_BF16) return SK_ERR_BAD_ARGUMENT;
+  if (w_layout != SK_WEIGHT_ROWMAJOR && w_layout != SK_WEIGHT_TILED) return SK_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(w_scale_f16) & 1) != 0) return SK_ERR_BAD_ALIGNMENT;
+  if (w_layout == SK_WEIGHT_TILED && (reinterpret_cast<uintptr_t>(w) & 15) != 0) return SK_ERR_BAD_ALIGNMENT;
+
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess) { (void)cudaGetLastError(); return SK_ERR_CUDA; }
+  if (device < 0 || device >= ndev) return SK_ERR_BAD_ARGUMENT;
+  int major = 0, sms = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return SK_ERR_CUDA;
+  }
+  if (major != 10) return SK_ERR_UNSUPPORTED_ARCH;
+
+  sk_w2a8_plan* plan = new (std::nothrow) sk_w2a8_plan();
+  if (!plan) return SK_ERR_OUT_OF_MEMORY;
+  plan->device = device;
+  plan->N = N; plan->K = K; plan->G = group_size; plan->zero_point = zero_point; plan->out_dtype = out_dtype;
+  plan->k_blocks = static_cast<int>((K + 127) / 128);
+  plan->n_tiles = static_cast<int>((N + 127) / 128);
+  plan->sm_count = sms;
+  plan->w_scale = static_cast<const __half*>(w_scale_f16);
+
+  int cur = -1;
+  cudaGetDevice(&cur);
+  cudaError_t e = cudaSetDevice(device);
+  int rc = SK_OK;
+  if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
+  if (rc == SK_OK) {
+    e = cudaMalloc(&plan->status, sizeof(int));
+    if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
+    else {
+      e = cudaMemset(plan->status, 0, sizeof(int));
+      if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
+    }
+  }
+  if (rc == SK_OK) {
+    if (w_layout == SK_WEIGHT_TILED) {
+      plan->w_tiled = w;
+    } else {
+      plan->w_rowmajor = w;
+      e = cudaMalloc(&plan->w_tiled_owned, static_cast<size_t>(sk_w2a8_tiled_bytes(N, K)));
+      if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
+      else {
+        rc = sk::repack_common(true, w, N, K, plan->w_tiled_owned, nullptr);
+        if (rc == SK_OK) {
+          e = cudaDeviceSynchronize();
+          if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
+        }
+        plan->w_tiled = plan->w_tiled_owned;
+      }
+    }
+  }
+  if (cur >= 0 && cur != device) (void)cudaSetDevice(cur);
+  if (rc != SK_OK) {
+    if (plan->status) cudaFree(plan->status);
+    if (plan->w_tiled_owned) cudaFree(plan->w_tiled_owned);
+    delete plan;
+    return rc;
+  }
+  *out = plan;
+  return SK_OK;
+}
+
+int sk_w2a8_plan_destroy(sk_w2a8_plan* plan) {
+  if (!plan) return SK_ERR_NULL_POINTER;
+  int cur = -1;
+  cudaGetDevice(&cur);
+  (void)cudaSetDevice(plan->device);
+  if (plan->status) cudaFree(plan->status);
+  if (plan->w_tiled_owned) cudaFree(plan->w_tiled_owned);
+  if (cur >= 0 && cur != plan->device) (void)cudaSetDevice(cur);
+  delete plan;
+  return SK_OK;
+}
+
+int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
+  if (!plan) return SK_ERR_NULL_POINTER;
+  switch (key) {
+    case SK_OPT_KERNEL:
+      if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
+      if (value == 2 && !plan->w_rowmajor) return SK_ERR_UNAVAILABLE;
+      plan->opt_kernel = static_cast<int>(value);
+      return SK_OK;
+    case SK_OPT_TOKEN_TILE:
+      if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_token_tile = static_cast<int>(value);
+      return SK_OK;
+    case SK_OPT_SPLIT_K:
+      if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_split_k = static_cast<int>(value);
+      return SK_OK;
+    default: return SK_ERR_BAD_ARGUMENT;
+  }
+}
+
+int sk_w2a8_gemm(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale, void* out,
+                 int64_t ld_out, sk_stream_t stream) {
+  return sk::run_gemm(plan, M, x_q, ld_x, x_scale, out, ld_out, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, int32_t* partials,
+                                sk_stream_t stream) {
+  if (!partials) return SK_ERR_NULL_POINTER;
+  return sk::run_gemm(plan, M, x_q, ld_x, nullptr, nullptr, 0, partials, static_cast<cudaStream_t>(stream));
+}
+
+int sk_w2a8_last_device_status(sk_w2a8_plan* plan, int* device_status) {
+  if (!plan || !device_status) return SK_ERR_NULL_POINTER;
+  int cur = -1;
+  cudaGetDevice(&cur);
+  (void)cudaSetDevice(plan->device);
+  int v = 0;
+  cudaError_t e = cudaMemcpy(&v, plan->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && v != 0) e = cudaMemset(plan->status, 0, sizeof(int));
+  if (cur >= 0 && cur != plan->device) (void)cudaSetDevice(cur);
+  if (e != cudaSuccess) return sk::cuda_fail(plan, e);
+  *device_status = v;
+  return v == 0 ? SK_OK : SK_ERR_DEVICE_TIMEOUT;
+}
+
+int sk_w2a8_last_cuda_error(const sk_w2a8_plan* plan) { return plan ? plan->last_cuda_error : 0; }
+
+int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* split_k, int* ctas, int* kernel_kind) {
+  if (!plan) return SK_ERR_NULL_POINTER;
+  if (M <= 0) return SK_ERR_BAD_SHAPE;
+  const sk::LaunchChoice c = sk::choose(plan, M);
+  if (token_tile) *token_tile = c.token_tile;
+  if (split_k) *split_k = c.split_k;
+  if (ctas) *ctas = static_cast<int>(plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile) * c.split_k);
+  if (kernel_kind) *kernel_kind = c.kernel;
+  return SK_OK;
+}
+
+}  // extern "C"

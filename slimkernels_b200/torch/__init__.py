@@ -1,0 +1,3 @@
+"""PyTorch-facing side of the W2A8 path: the op, the Linear/MLP modules and N-sharded execution."""
+from .ops import (W2A8Plan, load_extension, repack_weight, unrepack_weight, w2a8_gemm,  # noqa: F401
+                  w2a8_partials)

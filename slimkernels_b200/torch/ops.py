@@ -1,0 +1,116 @@
+"""`slimkernels::w2a8_gemm` and its plan object.
+
+The reference has no torch-facing quantised op (slimkernels/torch/llama.py only wraps HF generate);
+the call shape follows its notebook wrapper ``wint2_gemm(activation, weight, scale) -> out``
+(triton.ipynb:235-270): weights and scales in, a freshly allocated [M, N] tensor out, computed on the
+current CUDA stream.  All compute happens in lib/libsk_w2a8.so behind the C ABI; if the extension is not
+built or no sm_100 GPU is present the calls raise — there is no CPU or eager fallback.
+"""
+from __future__ import annotations
+
+import weakref
+
+import torch
+
+from .. import _build
+
+_loaded = False
+
+
+def load_extension() -> None:
+    """Loads lib/libsk_w2a8_torch.so (registers torch.ops.slimkernels.*).  Raises if it is not built."""
+    global _loaded
+    if _loaded:
+        return
+    import os
+    if not os.path.exists(_build.TORCH_LIB):
+        raise ImportError(f"{_build.TORCH_LIB} is not built; run `python -m slimkernels_b200._build`")
+    torch.ops.load_library(_build.TORCH_LIB)
+    _loaded = True
+
+
+class W2A8Plan:
+    """One weight matrix bound to its device (wraps sk_w2a8_plan).
+
+    w_packed uint8 [N, K/4] (matrix_packer layout) or, with ``tiled=True``, the 1-D output of
+    ``repack_weight``; w_scale float16 [K/G, N].  The tensors must stay alive as long as the plan.
+    """
+
+    def __init__(self, w, w_scale, N=None, K=None, group_size=128, zero_point=1, out_dtype=torch.float16,
+                 tiled=False):
+        load_extension()
+        if not tiled:
+            N, K = w.shape[0], w.shape[1] * 4
+        if out_dtype not in (torch.float16, torch.bfloat16):
+            raise TypeError("out_dtype must be torch.float16 or torch.bfloat16")
+        self.N, self.K, self.group_size, self.zero_point = int(N), int(K), int(group_size), int(zero_point)
+        self.out_dtype, self.tiled = out_dtype, tiled
+        self._w, self._w_scale = w, w_scale          # keep the device buffers alive
+        self._bf16 = out_dtype == torch.bfloat16
+        self._h = torch.ops.slimkernels.w2a8_plan_create(w, w_scale, self.N, self.K, self.group_size,
+                                                         self.zero_point, self._bf16, tiled)
+        self._fin = weakref.finalize(self, _destroy, self._h)
+
+    def set_option(self, key: int, value: int) -> None:
+        torch.ops.slimkernels.w2a8_plan_set_option(self._h, key, value)
+
+    def gemm(self, x_q, x_scale, out=None):
+        if out is None:
+            return torch.ops.slimkernels.w2a8_plan_gemm(self._h, x_q, x_scale, self.N, self.K, self._bf16)
+        torch.ops.slimkernels.w2a8_plan_gemm_out(self._h, x_q, x_scale, out, self.K)
+        return out
+
+    def partials(self, x_q):
+        return torch.ops.slimkernels.w2a8_plan_partials(self._h, x_q, self.N, self.K, self.group_size)
+
+    def device_status(self) -> int:
+        return torch.ops.slimkernels.w2a8_plan_device_status(self._h)
+
+
+def _destroy(handle):
+    try:
+        torch.ops.slimkernels.w2a8_plan_destroy(handle)
+    except Exception:
+        pass
+
+
+# plans of the functional op, keyed by the identity of the weight tensor and dropped with it
+_plan_cache: dict = {}
+
+
+def _cached_plan(w_packed, w_scale, group_size, zero_point, out_dtype) -> W2A8Plan:
+    key = (id(w_packed), id(w_scale), group_size, zero_point, out_dtype)
+    ent = _plan_cache.get(key)
+    ver = (w_packed._version, w_scale._version, w_packed.data_ptr(), w_scale.data_ptr())
+    if ent is not None and ent[0] == ver:
+        return ent[1]
+    plan = W2A8Plan(w_packed, w_scale, group_size=group_size, zero_point=zero_point, out_dtype=out_dtype)
+    _plan_cache[key] = (ver, plan)
+    weakref.finalize(w_packed, _plan_cache.pop, key, None)
+    return plan
+
+
+def w2a8_gemm(x_q, x_scale, w_packed, w_scale, group_size: int = 128, zero_point: int = 1,
+              out_dtype=torch.float16):
+    """out[M, N] = x_scale[:, None] * sum_g w_scale[g] * (x_q[:, g] @ (codes[:, g] - zero_point).T).
+
+    x_q int8 [M, K], x_scale float32 [M], w_packed uint8 [N, K/4] (first code of a byte in bits 7:6),
+    w_scale float16 [K/group_size, N].  The plan (tiled weight copy) is built on first use of a weight
+    tensor and reused while that tensor object is alive and unmodified.
+    """
+    return _cached_plan(w_packed, w_scale, group_size, zero_point, out_dtype).gemm(x_q, x_scale)
+
+
+def w2a8_partials(x_q, w_packed, w_scale, group_size: int = 128, zero_point: int = 1):
+    """int32 [K/G, M, N]: the exact per-group integer partial sums the GEMM scales and adds."""
+    return _cached_plan(w_packed, w_scale, group_size, zero_point, torch.float16).partials(x_q)
+
+
+def repack_weight(w_packed):
+    load_extension()
+    return torch.ops.slimkernels.w2a8_repack(w_packed)
+
+
+def unrepack_weight(w_tiled, N: int, K: int):
+    load_extension()
+    return torch.ops.slimkernels.w2a8_unrepack(w_tiled, N, K)

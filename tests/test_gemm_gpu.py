@@ -1,0 +1,205 @@
+"""Parity of the sm_100a W2A8 GEMM with the CPU oracle, through the C ABI.
+
+Bars: per-group int32 partial sums bit-exact; outputs within 1e-2 max-abs of the fp32 dequantise-then-matmul
+reference path (plus half an output ulp is already inside that bound for these value ranges).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import w2a8_oracle as O
+from slimkernels_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2   # max-abs vs fp32 dequant-matmul, stated by the benchmark spec
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(built_libs):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests selected but no CUDA device is visible")
+    assert torch.cuda.get_device_capability(0)[0] == 10, "these kernels are sm_100a only"
+
+
+from gpu_util import DeviceProblem, random_problem, to_np  # noqa: E402
+
+
+def _check(prob_np, G=128, zp=1, dtype=torch.float16, force=None, ld_out=None, check_partials=True):
+    x_q, xs, wp, ws = prob_np
+    dp = DeviceProblem(x_q, xs, wp, ws, G, zp, dtype)
+    if force:
+        dp.force(**force)
+    y = to_np(dp.gemm(ld_out=ld_out))
+    y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp, ws, G, zp)
+    N = wp.shape[0]
+    err = np.abs(y[:, :N] - y_ref).max()
+    tol = TOL if dtype == torch.float16 else TOL + np.abs(y_ref).max() * 2.0 ** -8
+    assert np.isfinite(y[:, :N]).all()
+    assert err <= tol, f"max abs err {err}"
+    if ld_out:
+        assert np.isnan(y[:, N:]).all(), "wrote outside the N columns"
+    if check_partials:
+        p = to_np(dp.partials())
+        np.testing.assert_array_equal(p, O.w2a8_partials(x_q, wp, G, zp))
+    return err
+
+
+def test_golden_vectors(golden):
+    i = 0
+    while f"gemm{i}_shape" in golden.files:
+        M, N, K, G = (int(v) for v in golden[f"gemm{i}_shape"])
+        x_q, xs = golden[f"gemm{i}_x_q"], golden[f"gemm{i}_x_scale"]
+        wp, ws = golden[f"gemm{i}_w_packed"], golden[f"gemm{i}_w_scale"]
+        if K % 32 == 0:
+            dp = DeviceProblem(x_q, xs, wp, ws, G, 1)
+            y = to_np(dp.gemm())
+            assert np.abs(y - golden[f"gemm{i}_y_ref"]).max() <= TOL
+            np.testing.assert_array_equal(to_np(dp.partials()), golden[f"gemm{i}_partials_zp1"])
+        i += 1
+    assert i >= 6
+
+
+@pytest.mark.parametrize("zp", [1, 2])
+def test_config0_full(zp):
+    """Benchmark config 0: M=16, N=K=4096, G=128, seed 0."""
+    from slimkernels_b200 import workloads as W
+    prob = W.make_problem(16, 4096, 4096, 128, seed=0)
+    _check(prob, 128, zp)
+
+
+@pytest.mark.parametrize("token_tile", [16, 32, 64, 128])
+@pytest.mark.parametrize("split_k", [1, 2, 4, 8])
+def test_every_tile_and_split(token_tile, split_k):
+    if token_tile == 128 and split_k > 1:
+        pytest.skip("split-K is for small token tiles")
+    M = {16: 13, 32: 32, 64: 70, 128: 200}[token_tile]
+    prob = random_problem(M, 384, 1024, 128, seed=token_tile + split_k)
+    _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, split_k=split_k))
+
+
+@pytest.mark.parametrize("M,N,K,G", [
+    (1, 128, 128, 128), (1, 8, 32, 32), (7, 130, 256, 128), (33, 200, 384, 128), (5, 136, 352, 32),
+    (16, 264, 512, 64), (9, 128, 768, 256), (129, 257, 1408, 128), (300, 1000, 640, 128),
+])
+def test_ragged_shapes(M, N, K, G):
+    _check(random_problem(M, N, K, G, seed=M + N + K))
+
+
+def test_checker_kernel_matches_oracle():
+    prob = random_problem(19, 200, 512, 128, seed=5)
+    _check(prob, force=dict(kernel=capi.KERNEL_CUDA_CORE))
+
+
+def test_wider_output_buffer_and_padded_activation_rows():
+    x_q, xs, wp, ws = random_problem(24, 256, 512, 128, seed=9)
+    _check((x_q, xs, wp, ws), ld_out=256 + 64, check_partials=False)
+    dp = DeviceProblem(x_q, xs, wp, ws, ld_x=512 + 64)
+    y = to_np(dp.gemm())
+    assert np.abs(y - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+
+
+def test_bf16_output():
+    _check(random_problem(40, 256, 512, 128, seed=3), dtype=torch.bfloat16, check_partials=False)
+
+
+def test_extreme_codes_and_activations():
+    """All-max / all-min operands reach the partial-sum bound 128*127*2 without overflow or saturation."""
+    M, N, K = 16, 128, 256
+    for code_byte, xv, zp in [(0xFF, 127, 1), (0x00, -127, 1), (0x00, 127, 2), (0xFF, -127, 2)]:
+        x_q = np.full((M, K), xv, dtype=np.int8)
+        xs = np.full((M,), 0.01, dtype=np.float32)
+        wp = np.full((N, K // 4), code_byte, dtype=np.uint8)
+        ws = np.full((K // 128, N), 0.005, dtype=np.float16)
+        dp = DeviceProblem(x_q, xs, wp, ws, 128, zp)
+        np.testing.assert_array_equal(to_np(dp.partials()), O.w2a8_partials(x_q, wp, 128, zp))
+        assert np.abs(to_np(dp.gemm()) - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws, 128, zp)).max() <= TOL
+
+
+def test_repack_round_trip_on_device():
+    from slimkernels_b200 import format as F
+    lib = capi.load()
+    rng = np.random.default_rng(2)
+    for N, K in [(128, 128), (200, 160), (5, 32), (1000, 1408)]:
+        wp = rng.integers(0, 256, size=(N, K // 4), dtype=np.uint8)
+        d_wp = torch.from_numpy(wp).cuda()
+        nbytes = lib.sk_w2a8_tiled_bytes(N, K)
+        assert nbytes == F.tiled_nbytes(N, K)
+        d_t = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        assert lib.sk_w2a8_repack(d_wp.data_ptr(), N, K, d_t.data_ptr(), None) == 0
+        np.testing.assert_array_equal(d_t.cpu().numpy(), F.repack_tiled(wp))
+        d_back = torch.zeros_like(d_wp)
+        assert lib.sk_w2a8_unrepack(d_t.data_ptr(), N, K, d_back.data_ptr(), None) == 0
+        np.testing.assert_array_equal(O.unpack_matrix(d_back.cpu().numpy()), O.unpack_matrix(wp))
+
+
+def test_plan_from_tiled_weights():
+    x_q, xs, wp, ws = random_problem(16, 256, 512, 128, seed=21)
+    lib = capi.load()
+    d_wp = torch.from_numpy(wp).cuda()
+    d_t = torch.empty(lib.sk_w2a8_tiled_bytes(256, 512), dtype=torch.uint8, device="cuda")
+    assert lib.sk_w2a8_repack(d_wp.data_ptr(), 256, 512, d_t.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    d_ws = torch.from_numpy(ws).cuda()
+    plan = capi.Plan(0, 256, 512, 128, 1, d_t.data_ptr(), d_ws.data_ptr(), w_layout=capi.SK_WEIGHT_TILED)
+    d_x, d_xs = torch.from_numpy(x_q).cuda(), torch.from_numpy(xs).cuda()
+    out = torch.empty(16, 256, dtype=torch.float16, device="cuda")
+    plan.gemm(16, d_x.data_ptr(), 512, d_xs.data_ptr(), out.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert np.abs(to_np(out) - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+    with pytest.raises(capi.SkError):
+        plan.set_option(capi.SK_OPT_KERNEL, capi.KERNEL_CUDA_CORE)   # needs the row-major bytes
+
+
+def test_argument_errors_on_device():
+    x_q, xs, wp, ws = random_problem(4, 128, 128, 128, seed=1)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    lib = capi.load()
+    out = torch.empty(4, 128, dtype=torch.float16, device="cuda")
+    h = dp.plan.handle
+    assert lib.sk_w2a8_gemm(h, 0, dp.x_q.data_ptr(), 128, dp.x_scale.data_ptr(), out.data_ptr(), 128, None) == capi.SK_ERR_BAD_SHAPE
+    assert lib.sk_w2a8_gemm(h, 4, dp.x_q.data_ptr(), 64, dp.x_scale.data_ptr(), out.data_ptr(), 128, None) == capi.SK_ERR_BAD_SHAPE
+    assert lib.sk_w2a8_gemm(h, 4, dp.x_q.data_ptr(), 128, dp.x_scale.data_ptr(), out.data_ptr(), 64, None) == capi.SK_ERR_BAD_SHAPE
+    assert lib.sk_w2a8_gemm(h, 4, dp.x_q.data_ptr() + 1, 128, dp.x_scale.data_ptr(), out.data_ptr(), 128, None) == capi.SK_ERR_BAD_ALIGNMENT
+    assert lib.sk_w2a8_gemm(h, 4, dp.x_q.data_ptr(), 136, dp.x_scale.data_ptr(), out.data_ptr(), 128, None) == capi.SK_ERR_BAD_ALIGNMENT
+    assert lib.sk_w2a8_gemm(h, 4, None, 128, dp.x_scale.data_ptr(), out.data_ptr(), 128, None) == capi.SK_ERR_NULL_POINTER
+
+
+def test_decode_shapes_property_linearity():
+    """Llama-2-7B decode shapes at full size: GPU tcgen05 kernel == GPU checker kernel bit for bit on the
+    integer partials, and y(x1 + x2) == y(x1) + y(x2) for activations that stay in int8 range."""
+    from slimkernels_b200 import workloads as W
+    for name, (N, K) in W.LLAMA2_7B_SHAPES.items():
+        x_q, xs, wp, ws = random_problem(32, N, K, 128, seed=N % 97)
+        x_q = (x_q // 2).astype(np.int8)
+        dp = DeviceProblem(x_q, xs, wp, ws)
+        p_tc = dp.partials()
+        dp.force(kernel=capi.KERNEL_CUDA_CORE)
+        p_cc = dp.partials()
+        assert torch.equal(p_tc, p_cc), name
+        dp.force()
+        # linearity on the integer level: P(x) + P(x') == P(x + x')
+        x2 = np.roll(x_q, 1, axis=0)
+        dp2 = DeviceProblem(x2, xs, wp, ws)
+        dps = DeviceProblem((x_q + x2).astype(np.int8), xs, wp, ws)
+        assert torch.equal(p_tc + dp2.partials(), dps.partials()), name
+        # sampled rows against the CPU oracle
+        rows = np.array([0, 1, N // 2, N - 1])
+        y = to_np(dp.gemm())
+        y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp[rows], ws[:, rows])
+        assert np.abs(y[:, rows] - y_ref).max() <= TOL, name
+
+
+def test_prefill_shape_against_checker_and_sampled_oracle():
+    """M=2048, N=K=8192 (benchmark config 2, smallest M): full output vs the CUDA-core checker kernel, sampled
+    output columns vs the CPU oracle."""
+    M, N, K = 2048, 8192, 8192
+    x_q, xs, wp, ws = random_problem(M, N, K, 128, seed=42)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    y = dp.gemm()
+    dp.force(kernel=capi.KERNEL_CUDA_CORE)
+    y_cc = dp.gemm()
+    assert (y.float() - y_cc.float()).abs().max().item() <= 2e-3
+    cols = np.arange(0, N, 509)
+    y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp[cols], ws[:, cols])
+    assert np.abs(to_np(y)[:, cols] - y_ref).max() <= TOL
