@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the W2A8 GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-sweeps]
+
+Headline workload (every N): the Llama-3-70B fused gate+up projection, M=4096 tokens, N=57344, K=8192,
+group 128, fp16 output; weights N-sharded over the ranks, fp16 output all-gathered with NCCL ("strong"
+scaling: total work fixed).  One step = one GEMM (+ all-gather when N > 1).  value = 2*M*N*K / time.
+
+At N=1 rank 0 additionally reports (outside the timed region) the decode sweep (Llama-2-7B shapes,
+M in {1,4,8,16,32}, HBM GB/s over packed-weight + scale bytes) and the prefill sweep (M in {2048,4096,8192},
+N=K=8192, int8 TOPS), and times the CPU restatement of the reference path on a bounded sample.
+
+`--impl reference` times the reference's CPU route (unpack_matrix -> dequantize_from_uint2 -> fp32 matmul,
+all host threads) on a bounded N-slab of the same workload; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "w2a8_gemm_tops"
+UNIT = "TOPS"
+WORKLOAD = dict(name="llama3_70b_gate_up_prefill", M=4096, N=57344, K=8192, G=128)
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                        bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                        source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU restatement of the reference path (oracle), timed on the host cores
+# --------------------------------------------------------------------------------------------------
+def cpu_reference_step(x_q, x_scale, w_packed, w_scale, G):
+    """unpack_matrix -> dequantize_from_uint2 -> fp32 matmul (torch, all threads).  Returns seconds."""
+    import torch
+    from oracle import w2a8_oracle as O
+    t0 = time.perf_counter()
+    codes = O.unpack_matrix(w_packed)
+    wdq = O.dequantize_from_uint2(np.ascontiguousarray(codes.T), w_scale, G)
+    xs = torch.from_numpy(x_q).float() * torch.from_numpy(x_scale)[:, None]
+    y = xs @ torch.from_numpy(wdq).float()
+    _ = y.to(torch.float16)
+    return time.perf_counter() - t0
+
+
+def cpu_sample(n_slab: int):
+    from slimkernels_b200 import workloads as W
+    M, K, G = WORKLOAD["M"], WORKLOAD["K"], WORKLOAD["G"]
+    rng = np.random.default_rng(0)
+    x_q, x_scale = W.make_activation(M, K, rng=rng)
+    w_packed = rng.integers(0, 256, size=(n_slab, K // 4), dtype=np.uint8)
+    w_scale = rng.uniform(0.001, 0.01, size=(K // G, n_slab)).astype(np.float16)
+    return x_q, x_scale, w_packed, w_scale
+
+
+def run_cpu_baseline(n_slab=2048, reps=2):
+    import torch
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x_q, x_scale, w_packed, w_scale = cpu_sample(n_slab)
+    best = min(cpu_reference_step(x_q, x_scale, w_packed, w_scale, WORKLOAD["G"]) for _ in range(reps))
+    ops = 2.0 * WORKLOAD["M"] * n_slab * WORKLOAD["K"]
+    return {"value": ops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "seconds_per_sample": best,
+            "sample": f"M={WORKLOAD['M']} x N-slab {n_slab} of {WORKLOAD['N']} x K={WORKLOAD['K']}: "
+                      f"unpack_matrix + dequantize_from_uint2 (numpy) + fp32 matmul (torch, {cores} threads), best of {reps}"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n_slab = 1024
+    x_q, x_scale, w_packed, w_scale = cpu_sample(n_slab)
+    for _ in range(args.warmup):
+        cpu_reference_step(x_q, x_scale, w_packed, w_scale, WORKLOAD["G"])
+    t = [cpu_reference_step(x_q, x_scale, w_packed, w_scale, WORKLOAD["G"]) for _ in range(args.steps)]
+    total = sum(t)
+    ops = 2.0 * WORKLOAD["M"] * n_slab * WORKLOAD["K"] * args.steps
+    value = ops / total / 1e12
+    sample = (f"each step = M={WORKLOAD['M']} x N-slab {n_slab} of {WORKLOAD['N']} x K={WORKLOAD['K']}, reference CPU route "
+              f"(unpack_matrix + dequantize_from_uint2 in numpy, fp32 matmul in torch) restated in oracle/")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config_dict(args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(n_gpus):
+    return {"workload": f"{WORKLOAD['name']}: M={WORKLOAD['M']} N={WORKLOAD['N']} K={WORKLOAD['K']} G={WORKLOAD['G']} "
+                        f"int8 x 2-bit -> fp16, seed 0 synthetic (benchmark config 3, gate+up)",
+            "parallelism": f"N-sharded x{n_gpus} + NCCL all-gather" if n_gpus > 1 else "single GPU",
+            "l2": "inputs larger than L2 (weights 117 MB + activations 34 MB + output 470 MB per step)"}
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def time_events(fn, iters, stream):
+    import torch
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(stream)
+    for _ in range(iters):
+        fn()
+    e.record(stream)
+    e.synchronize()
+    return s.elapsed_time(e) / iters   # ms
+
+
+def decode_sweep(dev, peaks):
+    """Llama-2-7B decode shapes: CUDA graph of 64 GEMMs cycling weight copies that total > 2x L2."""
+    import torch
+    from slimkernels_b200 import workloads as W
+    from slimkernels_b200.torch import W2A8Plan
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    out = []
+    rng = np.random.default_rng(0)
+    for name, (N, K) in W.LLAMA2_7B_SHAPES.items():
+        G = 128
+        wbytes = N * K // 4 + (K // G) * N * 2
+        ncopies = min(64, max(2, int(np.ceil(2.0 * l2 / wbytes)) + 1))
+        plans = []
+        for _ in range(ncopies):
+            wp = torch.from_numpy(rng.integers(0, 256, size=(N, K // 4), dtype=np.uint8)).to(dev)
+            ws = torch.from_numpy(rng.uniform(0.001, 0.01, size=(K // G, N)).astype(np.float16)).to(dev)
+            wt = torch.ops.slimkernels.w2a8_repack(wp)
+            torch.cuda.synchronize(dev)
+            plans.append(W2A8Plan(wt, ws, N=N, K=K, group_size=G, tiled=True))
+            del wp
+        for M in W.DECODE_M:
+            x_q = torch.from_numpy(rng.integers(-127, 128, size=(M, K), dtype=np.int8)).to(dev)
+            xs = torch.from_numpy(rng.uniform(0.005, 0.02, size=(M,)).astype(np.float32)).to(dev)
+            outs = [torch.empty(M, N, dtype=torch.float16, device=dev) for _ in range(2)]
+            calls = 64
+            st = torch.cuda.Stream(dev)
+            with torch.cuda.stream(st):
+                for i in range(min(ncopies, 4)):
+                    plans[i].gemm(x_q, xs, out=outs[i % 2])
+                st.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    for i in range(calls):
+                        plans[i % ncopies].gemm(x_q, xs, out=outs[i % 2])
+                for _ in range(3):
+                    g.replay()
+                st.synchronize()
+                ms_graph = time_events(g.replay, 10, st) / calls
+                # single launches of one plan, back to back (L2-warm, launch-bound): reported for context
+                ms_single = time_events(lambda: plans[0].gemm(x_q, xs, out=outs[0]), 50, st)
+            us = ms_graph * 1e3
+            gbs = wbytes / (ms_graph * 1e-3) / 1e9
+            out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(us, 3), "gbs": round(gbs, 1),
+                        "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "us_single_launch_l2_warm": round(ms_single * 1e3, 3),
+                        "weight_copies": ncopies, "algorithmic_bytes": wbytes})
+        del plans
+        torch.cuda.empty_cache()
+    return out
+
+
+def prefill_sweep(dev, peaks):
+    import torch
+    from slimkernels_b200 import workloads as W
+    from slimkernels_b200.torch import W2A8Plan
+    rng = np.random.default_rng(0)
+    N, K = W.PREFILL_NK
+    G = 128
+    wp = torch.from_numpy(rng.integers(0, 256, size=(N, K // 4), dtype=np.uint8)).to(dev)
+    ws = torch.from_numpy(rng.uniform(0.001, 0.01, size=(K // G, N)).astype(np.float16)).to(dev)
+    plan = W2A8Plan(wp, ws, group_size=G)
+    out = []
+    st = torch.cuda.current_stream(dev)
+    for M in W.PREFILL_M:
+        x_q = torch.from_numpy(rng.integers(-127, 128, size=(M, K), dtype=np.int8)).to(dev)
+        xs = torch.from_numpy(rng.uniform(0.005, 0.02, size=(M,)).astype(np.float32)).to(dev)
+        y = torch.empty(M, N, dtype=torch.float16, device=dev)
+        for _ in range(3):
+            plan.gemm(x_q, xs, out=y)
+        torch.cuda.synchronize(dev)
+        ms = time_events(lambda: plan.gemm(x_q, xs, out=y), 20, st)
+        tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+        out.append({"M": M, "N": N, "K": K, "us": round(ms * 1e3, 2), "tops": round(tops, 1),
+                    "frac_of_2x_bf16_burst": round(tops / (2 * peaks["bf16_tflops"]), 4),
+                    "frac_of_2x_bf16_sustained": round(tops / (2 * peaks["bf16_tflops_sustained"]), 4),
+                    "frac_of_nominal_4500": round(tops / 4500.0, 4)})
+    # library int8 GEMM on the same box, for context (cuBLASLt through torch._int_mm): not our kernel
+    try:
+        a = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device=dev)
+        b = torch.randint(-2, 2, (8192, 8192), dtype=torch.int8, device=dev).t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize(dev)
+        ms = time_events(lambda: torch._int_mm(a, b), 20, st)
+        lib_tops = 2.0 * 8192 ** 3 / (ms * 1e-3) / 1e12
+    except Exception:
+        lib_tops = None
+    return out, lib_tops
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from slimkernels_b200 import workloads as W
+    from slimkernels_b200.torch import load_extension
+    from slimkernels_b200.torch.sharded import ShardedW2A8Gemm, shard_bounds
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device visible; the W2A8 path has no CPU fallback")
+    load_extension()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py: --gpus N > 1 must be launched with torch.distributed.run")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = read_peaks()
+
+    M, N, K, G = WORKLOAD["M"], WORKLOAD["N"], WORKLOAD["K"], WORKLOAD["G"]
+    lo, hi = shard_bounds(N, world, rank)
+    n_local = hi - lo
+    rng_w = np.random.default_rng([0, rank])                    # each rank draws its own slice
+    wp = torch.from_numpy(rng_w.integers(0, 256, size=(n_local, K // 4), dtype=np.uint8)).to(dev)
+    ws = torch.from_numpy(rng_w.uniform(0.001, 0.01, size=(K // G, n_local)).astype(np.float16)).to(dev)
+    x_q_np, x_scale_np = W.make_activation(M, K, seed=0)        # replicated activations
+    h_x = torch.from_numpy(x_q_np).pin_memory()
+    h_xs = torch.from_numpy(x_scale_np).pin_memory()
+    d_x, d_xs = h_x.to(dev), h_xs.to(dev)
+    op = ShardedW2A8Gemm(wp, ws, N, group_size=G)
+    h_out = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- warm-up
+    for _ in range(max(args.warmup, 3)):
+        op(d_x, d_xs)
+    barrier()
+
+    # ---- timed region: K steps, device-resident inputs
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        ms_step = time_events(lambda: op(d_x, d_xs), args.steps, stream)
+        barrier()
+    ms_step = max_over_ranks(ms_step)
+    clocks = clk.summary()
+    value = 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
+
+    # ---- dominant kernel alone (this rank's GEMM launch), CUDA events on the launching stream
+    barrier()
+    ms_kernel = max_over_ranks(time_events(lambda: op.local_gemm(d_x, d_xs), args.steps, stream))
+    tops_kernel = 2.0 * M * n_local * K / (ms_kernel * 1e-3) / 1e12
+    peak_int8 = 2.0 * peaks["bf16_tflops"]
+    roofline = {"bound": "tensor", "achieved": round(tops_kernel, 2), "peak": round(peak_int8, 1), "unit": "TOP/s",
+                "frac": round(tops_kernel / peak_int8, 4), "traffic": None,
+                "kernel": "w2a8_umma_kernel<128,...>", "ms_per_launch": round(ms_kernel, 4),
+                "peak_note": f"2 x {peaks['source']} bf16 burst TFLOP/s (no int8 figure is measured on this pool); "
+                             f"vs 2 x sustained: {round(tops_kernel / (2 * peaks['bf16_tflops_sustained']), 4)}; "
+                             f"vs nominal 4500: {round(tops_kernel / 4500.0, 4)}",
+                "algorithmic_ops_per_launch": 2.0 * M * n_local * K}
+
+    # ---- end to end: pinned host activations in, this rank's output slice back to the host, every step
+    def e2e_step():
+        d_x.copy_(h_x, non_blocking=True)
+        d_xs.copy_(h_xs, non_blocking=True)
+        y = op(d_x, d_xs)
+        src = y if world == 1 else y[:, lo:hi]
+        h_out.copy_(src, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(2, min(args.steps, 10))
+    ms_e2e = max_over_ranks(time_events(e2e_step, e2e_steps, stream))
+    barrier()
+    e2e = {"value": round(2.0 * M * N * K / (ms_e2e * 1e-3) / 1e12, 3), "unit": UNIT,
+           "h2d_bytes_per_step": int(world * (h_x.numel() + h_xs.numel() * 4)),
+           "d2h_bytes_per_step": int(M * N * 2), "ms_per_step": round(ms_e2e, 4),
+           "note": "per step: activations H2D from pinned memory on every rank, GEMM (+ all-gather), each rank's output slice D2H"}
+
+    line = {"metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int2 -> int32 -> fp32 scale -> fp16",
+            "data": "synthetic", "config": config_dict(world), "clocks": clocks, "e2e": e2e,
+            "gpu_launches": args.steps, "roofline": roofline, "peaks": peaks}
+
+    if world == 1 and not args.no_sweeps:
+        del op, wp, ws
+        torch.cuda.empty_cache()
+        line["decode_sweep"] = decode_sweep(dev, peaks)
+        pre, lib_tops = prefill_sweep(dev, peaks)
+        line["prefill_sweep"] = pre
+        line["library_int8_gemm_tops_8192"] = None if lib_tops is None else round(lib_tops, 1)
+    if world == 1 and rank == 0:
+        line["cpu_baseline"] = run_cpu_baseline()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweeps", action="store_true", help="skip the decode / prefill sweeps at N=1")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

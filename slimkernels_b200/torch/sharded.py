@@ -1,0 +1,70 @@
+"""N-sharded execution of one W2A8 GEMM across the GPUs of a node (one process per GPU).
+
+Output features are independent, so rank r owns rows [r*N/R, (r+1)*N/R) of w_packed and the matching
+columns of w_scale; activations are replicated; K is not split, so no reduction is needed.  The only
+exchange is an all-gather of the fp16/bf16 output over NVLink (NCCL through torch.distributed).
+The reference has no multi-GPU code; this is the one parallel strategy the W2A8 path needs.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .ops import W2A8Plan
+
+
+def shard_bounds(N: int, world: int, rank: int, multiple: int = 128):
+    """[lo, hi) of the output features rank owns: equal slices, which must be multiples of `multiple`."""
+    if N % (world * multiple) != 0:
+        raise ValueError(f"N={N} must be a multiple of world_size*{multiple}={world * multiple}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weight(w_packed, w_scale, world: int, rank: int):
+    """This rank's slice of (w_packed [N, K/4], w_scale [K/G, N]) as contiguous tensors."""
+    lo, hi = shard_bounds(w_packed.shape[0], world, rank)
+    return w_packed[lo:hi].contiguous(), w_scale[:, lo:hi].contiguous()
+
+
+class ShardedW2A8Gemm:
+    """Holds this rank's weight slice; ``forward`` returns the full [M, N] output on every rank."""
+
+    def __init__(self, w_packed_local, w_scale_local, N_total: int, group=None, group_size=128, zero_point=1,
+                 out_dtype=torch.float16):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.N_total = N_total
+        self.N_local = w_packed_local.shape[0]
+        assert self.N_local * self.world == N_total
+        self.out_dtype = out_dtype
+        self.plan = W2A8Plan(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
+                             out_dtype=out_dtype)
+        self._bufs = {}
+
+    def _buffers(self, M, device):
+        key = (M, device)
+        if key not in self._bufs:
+            local = torch.empty(M, self.N_local, dtype=self.out_dtype, device=device)
+            gathered = torch.empty(self.world, M, self.N_local, dtype=self.out_dtype, device=device)
+            full = torch.empty(M, self.N_total, dtype=self.out_dtype, device=device)
+            self._bufs[key] = (local, gathered, full)
+        return self._bufs[key]
+
+    def local_gemm(self, x_q, x_scale):
+        local, _, _ = self._buffers(x_q.shape[0], x_q.device)
+        return self.plan.gemm(x_q, x_scale, out=local)
+
+    def forward(self, x_q, x_scale):
+        M = x_q.shape[0]
+        local, gathered, full = self._buffers(M, x_q.device)
+        self.plan.gemm(x_q, x_scale, out=local)
+        if self.world == 1:
+            return local
+        dist.all_gather_into_tensor(gathered, local, group=self.group)
+        # [R, M, N/R] -> [M, R, N/R] == [M, N]
+        full.view(M, self.world, self.N_local).copy_(gathered.permute(1, 0, 2))
+        return full
+
+    __call__ = forward

@@ -83,7 +83,7 @@ def test_every_tile_and_split(token_tile, split_k):
     (16, 264, 512, 64), (9, 128, 768, 256), (129, 257, 1408, 128), (300, 1000, 640, 128),
 ])
 def test_ragged_shapes(M, N, K, G):
-    _check(random_problem(M, N, K, G, seed=M + N + K))
+    _check(random_problem(M, N, K, G, seed=M + N + K), G=G)
 
 
 def test_checker_kernel_matches_oracle():
