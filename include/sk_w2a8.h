@@ -57,14 +57,14 @@ typedef enum sk_weight_layout {
 /* Keys of sk_w2a8_set_option (testing / tuning; 0 or SK_AUTO restores the heuristic). */
 typedef enum sk_option {
   SK_OPT_KERNEL = 1,      /* 0 auto, 1 tcgen05 kernel, 2 CUDA-core checker kernel (needs SK_WEIGHT_ROWMAJOR) */
-  SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 */
+  SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 / 256 */
   SK_OPT_SPLIT_K = 3      /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
 } sk_option;
 
 /* -------- weight preparation ("Blackwell tile order") ------------------------------------------
  * The tcgen05 kernel streams weights in a tiled order: 128 output rows x 128 K-codes per 4 KiB block,
  * blocks of one 128-row tile contiguous along K, bit order inside each 32-bit word chosen so that 16
- * codes expand to 16 int8 bytes with four shift+mask pairs.  The repack is a pure permutation of the
+ * codes expand to 16 int8 bytes with four byte-permute look-ups.  The repack is a pure permutation of the
  * 2-bit codes (plus zero padding of N to 128 and K to 128); sk_w2a8_unrepack inverts it exactly.
  * Replaces nothing in the reference; anticipated there by its pre-tiled copy test
  * (slimkernels/cute/gemm/test_bc.cu:70-74). */

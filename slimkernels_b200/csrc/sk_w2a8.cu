@@ -17,7 +17,8 @@ namespace sk {
 // ------------------------------------------------------------------------------------------------
 // Tiled weight order.  Block (tile T, k-block B) is 4096 bytes at ((T * k_blocks + B) * 4096); inside it the
 // 32-bit word for (row r, 16-code chunk c) sits at byte (c / 4) * 2048 + r * 16 + (c % 4) * 4 and holds
-//   sum_{j=0..3} sum_{b=0..3} code[n = 128 T + r][k = 128 B + 16 c + 4 j + b] << (8 b + 2 j).
+//   sum_{j=0..3} sum_{b=0..3} code[n = 128 T + r][k = 128 B + 16 c + 4 j + b] << (4 b + 2 (j & 1) + 16 (j >> 1)),
+// i.e. nibble b of each 16-bit half holds two codes whose low 2 bits, after a mask, are byte-permute selectors.
 // The source byte for codes 4j..4j+3 of that chunk (matrix_packer order: first code in bits 7:6) is
 // w_packed[n][(128 B + 16 c) / 4 + j].
 // ------------------------------------------------------------------------------------------------
@@ -28,7 +29,7 @@ __device__ __forceinline__ uint32_t tiled_word_from_bytes(const uint8_t (&src)[4
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
       const uint32_t code = (src[j] >> (6 - 2 * b)) & 3u;
-      w |= code << (8 * b + 2 * j);
+      w |= code << (4 * b + 2 * (j & 1) + 16 * (j >> 1));
     }
   }
   return w;
@@ -78,7 +79,7 @@ __global__ void unrepack_kernel(const uint32_t* __restrict__ w_tiled, uint8_t* _
       if (k + 4 * j >= K) continue;
       uint32_t byte = 0;
 #pragma unroll
-      for (int b = 0; b < 4; ++b) byte |= ((w >> (8 * b + 2 * j)) & 3u) << (6 - 2 * b);
+      for (int b = 0; b < 4; ++b) byte |= ((w >> (4 * b + 2 * (j & 1) + 16 * (j >> 1))) & 3u) << (6 - 2 * b);
       w_packed[n * row_bytes + k / 4 + j] = static_cast<uint8_t>(byte);
     }
   }
@@ -184,15 +185,17 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   LaunchChoice c;
   c.kernel = plan->opt_kernel ? plan->opt_kernel : 1;
   if (plan->opt_token_tile) c.token_tile = plan->opt_token_tile;
-  else c.token_tile = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  else c.token_tile = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const int groups = static_cast<int>(plan->K / plan->G);
   if (plan->opt_split_k) c.split_k = plan->opt_split_k;
   else {
-    // Fill the machine: split the K range of a tile over a cluster while there are fewer tiles than ~2 per SM.
+    // Fill the machine in ONE wave: split the K range of a tile over a cluster while the CTAs still fit the
+    // resident capacity (2 CTAs per SM for token tiles <= 32, else 1) and every CTA keeps >= 4 groups.
     const long long tiles = plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile);
+    const long long capacity = static_cast<long long>(plan->sm_count) * (c.token_tile <= 32 ? 2 : 1);
     int s = 1;
     if (c.token_tile <= 64)
-      while (s < 8 && tiles * s < 2LL * plan->sm_count && groups / (2 * s) >= 2) s *= 2;
+      while (s < 8 && tiles * (2 * s) <= capacity && groups / (2 * s) >= 4) s *= 2;
     c.split_k = s;
   }
   if (c.split_k > groups) c.split_k = 1;
@@ -200,11 +203,11 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   return c;
 }
 
-template <int BLOCK_M, int LSTAGES, int ESTAGES, bool DUMP>
+template <int BLOCK_M, int EPI_WGS, int LSTAGES, int ESTAGES, bool DUMP>
 static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
                        cudaStream_t stream) {
-  using L = SmemLayout<BLOCK_M, LSTAGES, ESTAGES>;
-  auto kern = w2a8_umma_kernel<BLOCK_M, LSTAGES, ESTAGES, DUMP>;
+  using L = KernelTraits<BLOCK_M, EPI_WGS, LSTAGES, ESTAGES>;
+  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, LSTAGES, ESTAGES, DUMP>;
   static int configured_device_mask[64] = {0};
   if (plan->device < 64 && !configured_device_mask[plan->device]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -213,7 +216,7 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmPar
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan->n_tiles, m_tiles, split_k);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.blockDim = dim3(L::kThreads, 1, 1);
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -234,10 +237,11 @@ template <bool DUMP>
 static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const GemmParams& prm,
                          int m_tiles, int split_k, cudaStream_t stream) {
   switch (token_tile) {
-    case 16: return launch_umma<16, 8, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 32: return launch_umma<32, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 64: return launch_umma<64, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 128: return launch_umma<128, 4, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 16: return launch_umma<16, 1, 8, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 32: return launch_umma<32, 1, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 64: return launch_umma<64, 1, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 128: return launch_umma<128, 2, 4, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 256: return launch_umma<256, 2, 4, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
     default: return SK_ERR_BAD_ARGUMENT;
   }
 }
@@ -313,7 +317,6 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.N = static_cast<int>(plan->N);
       prm.K = static_cast<int>(plan->K);
       prm.k_blocks = plan->k_blocks;
-      prm.k_steps = static_cast<int>(plan->K / 32);
       prm.steps_per_group = plan->G / 32;
       prm.groups = static_cast<int>(plan->K / plan->G);
       prm.zero_point = plan->zero_point;
@@ -484,7 +487,8 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
       plan->opt_kernel = static_cast<int>(value);
       return SK_OK;
     case SK_OPT_TOKEN_TILE:
-      if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128) return SK_ERR_BAD_ARGUMENT;
+      if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128 && value != 256)
+        return SK_ERR_BAD_ARGUMENT;
       plan->opt_token_tile = static_cast<int>(value);
       return SK_OK;
     case SK_OPT_SPLIT_K:

@@ -97,9 +97,13 @@ def prepare_weight(weight_kn: np.ndarray, group_size: int = 128):
 # Tiled weight order consumed by the sm_100a kernel (a pure permutation of the 2-bit codes).
 # Block (tile T of 128 rows, k-block B of 128 codes) is 4096 bytes at (T * k_blocks + B) * 4096; the
 # little-endian 32-bit word of (row r, 16-code chunk c) sits at byte (c // 4) * 2048 + r * 16 + (c % 4) * 4
-# and holds  sum_{j,b} code[128 T + r, 128 B + 16 c + 4 j + b] << (8 b + 2 j).
+# and holds  sum_{j,b} code[128 T + r, 128 B + 16 c + 4 j + b] << (4 b + 2 (j & 1) + 16 (j >> 1)).
 # N is padded to a multiple of 128 and K to a multiple of 128 with code 0.
 # --------------------------------------------------------------------------------------------------
+_j, _b = np.arange(4)[:, None], np.arange(4)[None, :]
+_TILED_SHIFTS = (4 * _b + 2 * (_j & 1) + 16 * (_j >> 1)).astype(np.uint32)   # [j, b]
+
+
 def tiled_nbytes(N: int, K: int) -> int:
     return ((N + 127) // 128) * ((K + 127) // 128) * 4096
 
@@ -111,7 +115,7 @@ def repack_tiled(w_packed: np.ndarray) -> np.ndarray:
     codes = np.zeros((T * 128, B * 128), dtype=np.uint32)
     codes[:N, :K] = unpack_matrix(w_packed)
     c6 = codes.reshape(T, 128, B, 8, 4, 4)                       # [T, r, B, c, j, b]
-    shifts = (8 * np.arange(4)[None, :] + 2 * np.arange(4)[:, None]).astype(np.uint32)   # [j, b]
+    shifts = _TILED_SHIFTS
     words = (c6 << shifts).sum(axis=(4, 5), dtype=np.uint32)     # [T, r, B, c]
     words = words.reshape(T, 128, B, 2, 4).transpose(0, 2, 3, 1, 4)   # [T, B, half, r, c % 4]
     return np.ascontiguousarray(words).astype("<u4").view(np.uint8).reshape(-1)
@@ -122,7 +126,7 @@ def unrepack_tiled(w_tiled: np.ndarray, N: int, K: int) -> np.ndarray:
     T, B = (N + 127) // 128, (K + 127) // 128
     words = np.ascontiguousarray(w_tiled).view("<u4").reshape(T, B, 2, 128, 4).astype(np.uint32)
     words = words.transpose(0, 3, 1, 2, 4).reshape(T, 128, B, 8)  # [T, r, B, c]
-    shifts = (8 * np.arange(4)[None, :] + 2 * np.arange(4)[:, None]).astype(np.uint32)   # [j, b]
+    shifts = _TILED_SHIFTS
     codes = ((words[..., None, None] >> shifts) & 3).astype(np.uint8)   # [T, r, B, c, j, b]
     codes = codes.reshape(T * 128, B * 128)[:N, :K]
     return pack_matrix(np.ascontiguousarray(codes))

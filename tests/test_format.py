@@ -104,13 +104,13 @@ def test_tiled_repack_round_trip_against_matrix_packer(N, K):
     assert t.dtype == np.uint8 and t.size == F.tiled_nbytes(N, K)
     back = F.unrepack_tiled(t, N, K)
     np.testing.assert_array_equal(O.unpack_matrix(back), codes)
-    # word semantics the kernel relies on: 16 codes expand with four shift+mask pairs
+    # word semantics the kernel relies on: every nibble of a word holds two codes (byte-permute selectors)
     words = t.view("<u4")
     kb = (K + 127) // 128
     for (n, k0) in [(0, 0), (N - 1, ((K - 16) // 16) * 16), (N // 2, (K // 32) * 16)]:
         T, r, B, c = n // 128, n % 128, k0 // 128, (k0 % 128) // 16
         w = int(words[(T * kb + B) * 1024 + (c // 4) * 512 + r * 4 + (c % 4)])
-        got = [((w >> (2 * j)) >> (8 * b)) & 3 for j in range(4) for b in range(4)]
+        got = [(w >> (4 * b + 2 * (j & 1) + 16 * (j >> 1))) & 3 for j in range(4) for b in range(4)]
         assert got == [int(v) for v in codes[n, k0:k0 + 16]]
 
 

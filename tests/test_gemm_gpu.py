@@ -68,12 +68,12 @@ def test_config0_full(zp):
     _check(prob, 128, zp)
 
 
-@pytest.mark.parametrize("token_tile", [16, 32, 64, 128])
+@pytest.mark.parametrize("token_tile", [16, 32, 64, 128, 256])
 @pytest.mark.parametrize("split_k", [1, 2, 4, 8])
 def test_every_tile_and_split(token_tile, split_k):
-    if token_tile == 128 and split_k > 1:
+    if token_tile >= 128 and split_k > 1:
         pytest.skip("split-K is for small token tiles")
-    M = {16: 13, 32: 32, 64: 70, 128: 200}[token_tile]
+    M = {16: 13, 32: 32, 64: 70, 128: 200, 256: 300}[token_tile]
     prob = random_problem(M, 384, 1024, 128, seed=token_tile + split_k)
     _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, split_k=split_k))
 
@@ -97,6 +97,24 @@ def test_wider_output_buffer_and_padded_activation_rows():
     dp = DeviceProblem(x_q, xs, wp, ws, ld_x=512 + 64)
     y = to_np(dp.gemm())
     assert np.abs(y - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+
+
+@pytest.mark.parametrize("zp", [0, 3])
+def test_other_zero_points(zp):
+    """Zero points 0 and 3 reach |code - zp| = 3, which switches the accumulator bias to 2^16."""
+    _check(random_problem(20, 256, 512, 128, seed=zp), zp=zp)
+
+
+def test_many_groups_accuracy():
+    """K = 28672 (224 groups, the 70B down-projection depth): accumulated rounding stays inside the tolerance."""
+    x_q, xs, wp, ws = random_problem(48, 256, 28672, 128, seed=77)
+    for tile in (64, 256):
+        dp = DeviceProblem(x_q, xs, wp, ws).force(token_tile=tile)
+        y = to_np(dp.gemm())
+        y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)
+        assert np.abs(y - y_ref).max() <= TOL
+        # and well inside it, against the same arithmetic in fp32 on the CPU
+        assert np.abs(y - O.w2a8_gemm_int_path(x_q, xs, wp, ws)).max() <= 6e-3
 
 
 def test_bf16_output():
