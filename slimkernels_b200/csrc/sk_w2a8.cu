@@ -175,6 +175,10 @@ static int cuda_fail(sk_w2a8_plan* plan, cudaError_t e) {
   return e == cudaErrorMemoryAllocation ? SK_ERR_OUT_OF_MEMORY : SK_ERR_CUDA;
 }
 
+#ifdef SK_TRACE
+static long long* g_trace_buffer = nullptr;
+#endif
+
 struct LaunchChoice {
   int kernel;      // 1 tcgen05, 2 CUDA-core checker
   int token_tile;  // 16 / 32 / 64 / 128
@@ -203,11 +207,11 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   return c;
 }
 
-template <int BLOCK_M, int EPI_WGS, int LSTAGES, int ESTAGES, bool DUMP>
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP>
 static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
                        cudaStream_t stream) {
-  using L = KernelTraits<BLOCK_M, EPI_WGS, LSTAGES, ESTAGES>;
-  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, LSTAGES, ESTAGES, DUMP>;
+  using L = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>;
+  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, DUMP>;
   static int configured_device_mask[64] = {0};
   if (plan->device < 64 && !configured_device_mask[plan->device]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -233,15 +237,38 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmPar
   return SK_OK;
 }
 
+constexpr int kAccBufsSmall = 4;   // accumulator buffers of the token tiles <= 128
+constexpr int kAccBufs256 = 2;     // 2 x 256 columns fill the tensor memory
+static int acc_bufs_of(int token_tile) { return token_tile == 256 ? kAccBufs256 : kAccBufsSmall; }
+
+// The running sum of one accumulator buffer must stay inside (-2^22, 2^22):
+// (K handled per buffer) * 127 * max|code - zp| < 2^22.
+static bool running_sum_fits(const sk_w2a8_plan* plan, int token_tile, int split_k) {
+  const long long groups = plan->K / plan->G;
+  const long long groups_cta = (groups + split_k - 1) / split_k;
+  const int ab = acc_bufs_of(token_tile);
+  const long long k_per_buf = ((groups_cta + ab - 1) / ab) * plan->G;
+  const int mx = plan->zero_point > 3 - plan->zero_point ? plan->zero_point : 3 - plan->zero_point;
+  return k_per_buf * 127 * mx < (1LL << 22);
+}
+
+// partials[g] holds the running sum of its accumulator buffer; turn it into the group's own partial sum.
+__global__ void diff_partials_kernel(int32_t* __restrict__ partials, int groups, long long mn, int acc_bufs) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < mn;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    for (int g = groups - 1; g >= acc_bufs; --g) partials[g * mn + i] -= partials[(g - acc_bufs) * mn + i];
+}
+
 template <bool DUMP>
 static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const GemmParams& prm,
                          int m_tiles, int split_k, cudaStream_t stream) {
   switch (token_tile) {
-    case 16: return launch_umma<16, 1, 8, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 32: return launch_umma<32, 1, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 64: return launch_umma<64, 1, 6, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 128: return launch_umma<128, 2, 4, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 256: return launch_umma<256, 2, 4, 3, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    // <tokens, epilogue warpgroups, expander warps, load stages, expanded stages, accumulator buffers>
+    case 16: return launch_umma<16, 1, 4, 8, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 32: return launch_umma<32, 1, 4, 6, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 64: return launch_umma<64, 1, 4, 6, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 128: return launch_umma<128, 2, 4, 4, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 256: return launch_umma<256, 2, 4, 4, 3, kAccBufs256, DUMP>(plan, map, prm, m_tiles, split_k, stream);
     default: return SK_ERR_BAD_ARGUMENT;
   }
 }
@@ -288,6 +315,10 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
   }
   LaunchChoice ch = choose(plan, M);
   if (partials) ch.split_k = 1;
+  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k)) {
+    if (ch.token_tile == 256 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1)) ch.token_tile = 128;
+    else return SK_ERR_BAD_SHAPE;   // K too deep for the int32 running sums of this tile configuration
+  }
   int rc = SK_OK;
   if (ch.kernel == 2) {
     if (!plan->w_rowmajor) rc = SK_ERR_UNAVAILABLE;
@@ -321,9 +352,21 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.groups = static_cast<int>(plan->K / plan->G);
       prm.zero_point = plan->zero_point;
       prm.out_bf16 = plan->out_dtype == SK_OUT_BF16;
+#ifdef SK_TRACE
+      prm.trace = g_trace_buffer;
+#endif
       const int m_tiles = static_cast<int>((M + ch.token_tile - 1) / ch.token_tile);
       if (m_tiles > 65535) rc = SK_ERR_BAD_SHAPE;
-      else if (partials) rc = dispatch_umma<true>(plan, ch.token_tile, map, prm, m_tiles, 1, stream);
+      else if (partials) {
+        rc = dispatch_umma<true>(plan, ch.token_tile, map, prm, m_tiles, 1, stream);
+        if (rc == SK_OK) {
+          const long long mn = M * plan->N;
+          const int blocks = static_cast<int>(mn / 256 + 1 < 148 * 8 ? mn / 256 + 1 : 148 * 8);
+          diff_partials_kernel<<<blocks, 256, 0, stream>>>(partials, prm.groups, mn, acc_bufs_of(ch.token_tile));
+          e = cudaGetLastError();
+          if (e != cudaSuccess) rc = cuda_fail(plan, e);
+        }
+      }
       else rc = dispatch_umma<false>(plan, ch.token_tile, map, prm, m_tiles, ch.split_k, stream);
     }
   }
@@ -536,5 +579,13 @@ int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* sp
   if (kernel_kind) *kernel_kind = c.kernel;
   return SK_OK;
 }
+
+#ifdef SK_TRACE
+// Diagnostic build only: device buffer of 5 x 64 clock stamps written by CTA (0,0,0) of the next launches.
+int sk_w2a8_set_trace_buffer(long long* device_buffer) {
+  sk::g_trace_buffer = device_buffer;
+  return SK_OK;
+}
+#endif
 
 }  // extern "C"

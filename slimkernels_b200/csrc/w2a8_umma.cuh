@@ -1,26 +1,33 @@
 // The W2A8 GEMM kernel for sm_100a.
 //
 // One CTA computes a tile of 128 output features x BLOCK_M tokens over a range of scale groups:
-//   1. a producer thread brings, per 128-wide K block, one 4 KiB block of tiled 2-bit weights (bulk TMA copy)
+//   1. a producer warp brings, per 128-wide K block, one 4 KiB block of tiled 2-bit weights (bulk TMA copy)
 //      and one BLOCK_M x 128 int8 activation tile (tensor-map TMA, 128-byte swizzle) into a ring of shared
 //      memory stages guarded by mbarriers;
-//   2. one warpgroup of expander threads turns the 2-bit codes into int8 bytes (code - zero_point) with a
-//      byte-permute look-up (prmt), written straight into the 128-byte-swizzled K-major layout the tensor
-//      core reads;
-//   3. one thread issues tcgen05.mma kind::i8 (128 x BLOCK_M x 32 per instruction): the weights are the
+//   2. expander warps turn the 2-bit codes into int8 bytes (code - zero_point) with a byte-permute look-up
+//      (prmt), written straight into the 128-byte-swizzled K-major layout the tensor core reads;
+//   3. an MMA warp issues tcgen05.mma kind::i8 (128 x BLOCK_M x 32 per instruction): the weights are the
 //      "A"/M operand, the tokens the "B"/N operand, int32 accumulators live in tensor memory, one accumulator
-//      buffer per scale group (two buffers, so the next group accumulates while this one drains);
+//      buffer per scale group (ACC_BUFS buffers, so later groups accumulate while earlier ones drain);
 //   4. one or two epilogue warpgroups read each finished group from tensor memory (lane = output feature,
 //      column = token), multiply by that feature's group scale (a per-thread scalar) and accumulate in fp32;
 //      at the end the per-token activation scale is applied, the tile is transposed through shared memory
 //      and written with 16-byte coalesced stores.
 //
-// Integer -> float without a conversion instruction: every accumulator buffer is pre-set to a positive bias B
-// (2^15, or 2^16 when |code - zp| can reach 3) and the MMAs always accumulate, so a finished group holds
-// D = B + P with 0 < D < 2^23.  Read as an IEEE float, those bits are the denormal D * 2^-149, exactly.  The
-// epilogue therefore needs ONE fused multiply-add per value, acc += (s * 2^100) * asfloat(D); the bias term
-// B * sum_g s is the same for every token of a thread and is removed with one subtraction per 16 groups.
-// The exact partial sum P = D - B is what the debug entry point stores.
+// Integer -> float without a conversion instruction, and without ever resetting an accumulator:
+//   * every accumulator buffer is pre-set ONCE per tile to the bias B = 2^22 and the MMAs always accumulate, so
+//     after group g buffer b = g mod ACC_BUFS holds the running sum  D_g = B + sum_{g' <= g, g' = g mod ACC_BUFS} P_g'
+//     with 0 < D < 2^23 (the host refuses K ranges whose running sums could leave that interval);
+//   * read as an IEEE float those bits are the denormal D * 2^-149, exactly;
+//   * summation by parts turns  sum_g s_g P_g  into  sum_g (s_g - s_{g+ACC_BUFS}) (D_g - B)  (s = 0 past the
+//     end), so the epilogue needs ONE fused multiply-add per value, acc += ((s_g - s_{g+ACC_BUFS}) * 2^100) *
+//     asfloat(D_g); the B term is the same for every token of a thread and is removed once per 16 groups.
+// Re-setting a buffer per group instead (tcgen05.st) costs more tensor-memory write bandwidth than the whole
+// epilogue has to spare.  The debug entry point stores the running sums; the host differences them into P.
+//
+// The producer and MMA warps run their loops warp-uniformly (all lanes wait, one elected lane issues) and keep
+// the loop bodies short: a single warp retires dependent instructions several cycles apart, and the loop must
+// turn around in less than the tensor-core time of one K block.  mbarriers count one arrival per warp.
 //
 // With SPLIT_K > 1 the CTAs of one thread-block cluster split the groups of a tile and reduce their fp32
 // accumulators through distributed shared memory in a fixed order (deterministic, no global scratch).
@@ -37,10 +44,9 @@ namespace sk {
 
 constexpr int kTileN = 128;          // output features per CTA tile (MMA M)
 constexpr int kBlockK = 128;         // K codes per pipeline stage (= one 128-byte swizzle row of int8)
-constexpr int kStepK = 32;           // K per tcgen05.mma kind::i8
 constexpr int kWpBytes = kTileN * kBlockK / 4;   // 4096: tiled 2-bit block
 constexpr int kWxBytes = kTileN * kBlockK;       // 16384: expanded int8 block
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
+constexpr long long kWaitLimitCycles = 1000000000ll;  // every mbarrier wait gives up after 1e9 SM cycles (0.5-0.8 s)
 constexpr int kBiasFlushGroups = 16;  // the bias term is subtracted from the accumulators this often
 
 // device status codes: role * 16 + barrier kind
@@ -51,6 +57,17 @@ enum : int {
   kStEpilogueAccFull = 0x41,
   kStDrain = 0x51
 };
+
+// Optional in-kernel timeline (compiled only with -DSK_TRACE): CTA (0,0,0) stores SM clock stamps.
+#ifdef SK_TRACE
+#define SK_TRACE_EVENT(role, idx)                                                                 \
+  do {                                                                                            \
+    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 64)           \
+      p.trace[(role) * 64 + (idx)] = clock64();                                                   \
+  } while (0)
+#else
+#define SK_TRACE_EVENT(role, idx) do { } while (0)
+#endif
 
 struct GemmParams {
   const uint8_t* w_tiled;     // [n_tiles][k_blocks][4096]
@@ -66,22 +83,28 @@ struct GemmParams {
   int groups;                 // K / G
   int zero_point;
   int out_bf16;
+#ifdef SK_TRACE
+  long long* trace;           // [8][64] clock stamps of CTA (0,0,0)
+#endif
 };
 
-template <int BLOCK_M, int EPI_WGS, int LSTAGES, int ESTAGES>
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS>
 struct KernelTraits {
-  static constexpr int kThreads = (EPI_WGS + 2) * 128;
+  static constexpr int kEpiWarps = EPI_WGS * 4;
+  static constexpr int kWarps = ((kEpiWarps + EXP_WARPS + 2 + 3) / 4) * 4;   // whole warpgroups
+  static constexpr int kThreads = kWarps * 32;
   static constexpr int kEpiThreads = EPI_WGS * 128;
+  static constexpr int kRowsPerExpThread = 128 / (EXP_WARPS * 32);
   static constexpr int kColsPerWg = BLOCK_M / EPI_WGS;           // accumulators per epilogue thread
-  static constexpr int kChunk = (kColsPerWg >= 32 && kColsPerWg <= 64) ? 32 : 16;   // TMEM columns per tcgen05.ld
+  static constexpr int kChunk = kColsPerWg >= 32 ? 32 : 16;      // TMEM columns per tcgen05.ld
   static constexpr int kNumChunks = kColsPerWg / kChunk;
-  static constexpr uint32_t kTmemCols = (2 * BLOCK_M < 32) ? 32 : 2 * BLOCK_M;   // power of two >= 32
+  static constexpr uint32_t kTmemCols = (ACC_BUFS * BLOCK_M < 32) ? 32 : ACC_BUFS * BLOCK_M;
   static constexpr int kXBytes = BLOCK_M * kBlockK;
   static constexpr int kOffX = 0;
   static constexpr int kOffWx = kOffX + LSTAGES * kXBytes;
   static constexpr int kOffWp = kOffWx + ESTAGES * kWxBytes;
   static constexpr int kOffBar = kOffWp + LSTAGES * kWpBytes;
-  static constexpr int kNumBars = 2 * LSTAGES + 2 * ESTAGES + 4;
+  static constexpr int kNumBars = 2 * LSTAGES + 2 * ESTAGES + 2 * ACC_BUFS;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kOffXs = kOffMisc + 16;                   // fp32 [BLOCK_M]: x_scale of the tile's tokens
   static constexpr int kTotal = kOffXs + BLOCK_M * 4;
@@ -90,13 +113,29 @@ struct KernelTraits {
   // (fp32 [BLOCK_M][128] for the split-K reduction, 16-bit [BLOCK_M][128] otherwise).
   static_assert(BLOCK_M * kTileN * 4 <= kOffBar, "output staging must fit in the operand ring");
   static_assert(kColsPerWg % kChunk == 0 && kNumChunks >= 1, "bad epilogue split");
-  // Two epilogue warpgroups (512 threads, 128 registers each at launch): the epilogue warpgroups take registers
-  // from the expander / control warpgroups.  2 * 128 * (kEpiRegs + kOtherRegs) == 65536.
+  static_assert(EXP_WARPS == 2 || EXP_WARPS == 4, "expander warps");
+  static_assert((ACC_BUFS & (ACC_BUFS - 1)) == 0 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM");
+  // Register budgets.  With two epilogue warpgroups the epilogue threads hold kColsPerWg accumulators plus two
+  // sets of TMEM-load registers and take registers from the other warpgroup(s) with setmaxnreg.  The CTA's pool
+  // is what it was given at launch (kLaunchRegs per thread); setmaxnreg.inc BLOCKS until the pool can serve it,
+  // so the budgets must add up to no more than the pool or the kernel hangs:
+  //   BLOCK_M 256, 4 expander warps: 512 threads, 128 at launch -> epilogue 216, expanders 48, control 32
+  //   BLOCK_M 256, 2 expander warps: 384 threads, 168 at launch -> epilogue 224, expanders + control 56
+  //   BLOCK_M 128:                   512 threads, 128 at launch -> epilogue 168, others 88
   static constexpr bool kUseSetMaxNReg = (EPI_WGS == 2);
-  static constexpr int kEpiRegs = kColsPerWg > 64 ? 192 : 160;
-  static constexpr int kOtherRegs = 256 - kEpiRegs;
-  // Two register sets for TMEM loads (load chunk c+1 while chunk c is consumed) only where registers allow.
-  static constexpr bool kDoubleBuf = (kNumChunks > 1) && (EPI_WGS == 1);
+  static constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
+  static constexpr bool kBig = kColsPerWg > 64;
+  static constexpr int kEpiRegs = kBig ? (kThreads == 384 ? 224 : 216) : 168;
+  static constexpr int kExpRegs = kBig ? 48 : 88;                         // warpgroup holding the expander warps
+  static constexpr int kCtlRegs = kBig ? (kThreads == 384 ? 56 : 32) : 88;   // warpgroup holding producer + MMA warps
+  static constexpr int kExpWgThreads = (EXP_WARPS == 4) ? 128 : 0;        // expanders have a warpgroup of their own
+  static_assert(!kUseSetMaxNReg ||
+                    kEpiThreads * kEpiRegs + kExpWgThreads * kExpRegs +
+                            (kThreads - kEpiThreads - kExpWgThreads) * kCtlRegs <= kThreads * kLaunchRegs,
+                "setmaxnreg budgets exceed the registers the CTA owns");
+  // Load chunk c+1 from TMEM while chunk c is consumed (where registers allow: two warps per scheduler
+  // already overlap each other's load latency).
+  static constexpr bool kDoubleBuf = (kNumChunks > 1) && (kColsPerWg <= 64);
   static constexpr int kMinBlocks = (BLOCK_M <= 32) ? 2 : 1;
 };
 
@@ -105,19 +144,27 @@ struct WaitCtx {
   int* status;               // global
 };
 
+// Slow path of a bounded wait (inlined: a real call inside a kernel that re-partitions registers with setmaxnreg
+// does not compile); the fast path in wait_bounded is a single poll.
+// The limit is counted on the SM clock (%globaltimer costs about a microsecond per read).
+__device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const long long t0 = clock64();
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
 // Bounded wait.  Returns false if the limit expired here or in any other thread of the CTA.
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*ctx.abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      *ctx.abort_flag = 1;
-      atomicCAS(ctx.status, 0, code);
-      return false;
-    }
-  }
+  return wait_slow(bar, parity, ctx.abort_flag, ctx.status, code);
 }
 
 // 16 two-bit codes held in `w` as  sum_{j,b} code[4j+b] << (4b + 2(j&1) + 16(j>>1))  ->  16 int8 bytes
@@ -133,28 +180,39 @@ __device__ __forceinline__ uint4 expand16(uint32_t w, uint32_t lut) {
   return o;
 }
 
-template <int BLOCK_M, int EPI_WGS, int LSTAGES, int ESTAGES, bool DUMP>
-__global__ void __launch_bounds__((EPI_WGS + 2) * 128, (BLOCK_M <= 32 ? 2 : 1))
+template <int CHUNK>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&v)[CHUNK]) {
+  if constexpr (CHUNK == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
+}
+template <int CHUNK>
+__device__ __forceinline__ void tmem_fill_chunk(uint32_t taddr, uint32_t value) {
+  if constexpr (CHUNK == 32) tmem_st_fill_32x32(taddr, value); else tmem_st_fill_32x16(taddr, value);
+}
+
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP>
+__global__ void __launch_bounds__(KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>::kThreads,
+                                  KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>::kMinBlocks)
 w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-  using T = KernelTraits<BLOCK_M, EPI_WGS, LSTAGES, ESTAGES>;
+  using T = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>;
   constexpr int kChunk = T::kChunk;
   constexpr int kNumChunks = T::kNumChunks;
   constexpr int kCols = T::kColsPerWg;
   constexpr uint32_t kStageTxBytes = kWpBytes + T::kXBytes;
-  constexpr int kExpWarp0 = EPI_WGS * 4;        // first expander warp
-  constexpr int kProducerWarp = kExpWarp0 + 4;
+  constexpr int kExpWarp0 = T::kEpiWarps;       // first expander warp
+  constexpr int kProducerWarp = kExpWarp0 + EXP_WARPS;
   constexpr int kMmaWarp = kProducerWarp + 1;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_base + T::kOffBar;
-  auto bar_ld_full = [&](int i) { return bar_base + 8u * i; };
-  auto bar_ld_empty = [&](int i) { return bar_base + 8u * (LSTAGES + i); };
-  auto bar_ex_full = [&](int i) { return bar_base + 8u * (2 * LSTAGES + i); };
-  auto bar_ex_empty = [&](int i) { return bar_base + 8u * (2 * LSTAGES + ESTAGES + i); };
-  auto bar_acc_full = [&](int i) { return bar_base + 8u * (2 * LSTAGES + 2 * ESTAGES + i); };
-  auto bar_acc_empty = [&](int i) { return bar_base + 8u * (2 * LSTAGES + 2 * ESTAGES + 2 + i); };
+  // barrier addresses: consecutive 8-byte slots
+  const uint32_t bar_ld_full = bar_base;
+  const uint32_t bar_ld_empty = bar_ld_full + 8u * LSTAGES;
+  const uint32_t bar_ex_full = bar_ld_empty + 8u * LSTAGES;
+  const uint32_t bar_ex_empty = bar_ex_full + 8u * ESTAGES;
+  const uint32_t bar_acc_full = bar_ex_empty + 8u * ESTAGES;
+  const uint32_t bar_acc_empty = bar_acc_full + 8u * ACC_BUFS;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::kOffMisc + 4);
   const WaitCtx ctx{abort_flag, p.status};
@@ -177,14 +235,17 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
   const int kb_begin = ks_begin / 4;
   const int kb_end = (ks_end + 3) / 4;
 
-  // |code - zp| <= 2 keeps |P| <= 128*127*2 < 2^15; zero points 0 and 3 need the next power of two.
-  const uint32_t bias = (p.zero_point == 1 || p.zero_point == 2) ? 32768u : 65536u;
+  // running sums stay inside (-2^22, 2^22): checked on the host (kMaxKPerAccBuf)
+  const uint32_t bias = 1u << 22;
 
   // ---------------------------------------------------------------- set-up
+  if (threadIdx.x == 0) SK_TRACE_EVENT(4, 0);
+  // Every mbarrier counts ONE arrival per participating warp (lane 0, after __syncwarp): arrivals on one
+  // barrier are serialised shared-memory atomics.
   if (threadIdx.x == 0) {
-    for (int i = 0; i < LSTAGES; ++i) { mbar_init(bar_ld_full(i), 1); mbar_init(bar_ld_empty(i), 1 + 128); }
-    for (int i = 0; i < ESTAGES; ++i) { mbar_init(bar_ex_full(i), 128); mbar_init(bar_ex_empty(i), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full(i), 1); mbar_init(bar_acc_empty(i), T::kEpiThreads); }
+    for (int i = 0; i < LSTAGES; ++i) { mbar_init(bar_ld_full + 8 * i, 1); mbar_init(bar_ld_empty + 8 * i, 1 + EXP_WARPS); }
+    for (int i = 0; i < ESTAGES; ++i) { mbar_init(bar_ex_full + 8 * i, EXP_WARPS); mbar_init(bar_ex_empty + 8 * i, 1); }
+    for (int i = 0; i < ACC_BUFS; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -197,106 +258,178 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) SK_TRACE_EVENT(4, 1);
 
   if (warp >= kExpWarp0) {
-    if constexpr (T::kUseSetMaxNReg) setmaxnreg_dec<T::kOtherRegs>();
+    if constexpr (T::kUseSetMaxNReg) {
+      if (EXP_WARPS == 4 && warp < kProducerWarp) setmaxnreg_dec<T::kExpRegs>();
+      else setmaxnreg_dec<T::kCtlRegs>();
+    }
     if (warp == kProducerWarp) {
-      // ============================================================ producer
-      if (lane == 0) {
-        const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
-        int issued = 0;
-        bool ok = true;
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++issued) {
-          const int l = issued % LSTAGES;
-          const uint32_t ph = (issued / LSTAGES) & 1;
-          ok = wait_bounded(bar_ld_empty(l), ph ^ 1, ctx, kStProducerEmpty);
-          if (!ok) break;
-          mbar_arrive_expect_tx(bar_ld_full(l), kStageTxBytes);
-          bulk_load_1d(smem_base + T::kOffWp + l * kWpBytes, wsrc + static_cast<size_t>(issued) * kWpBytes,
-                       kWpBytes, bar_ld_full(l));
-          tma_load_2d(smem_base + T::kOffX + l * T::kXBytes, &tmap_x, kb * kBlockK, m0, bar_ld_full(l));
+      // ============================================================ producer (whole warp loops, one lane issues)
+      const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
+      uint32_t dst_wp = smem_base + T::kOffWp, dst_x = smem_base + T::kOffX;
+      uint32_t full = bar_ld_full, empty = bar_ld_empty;
+      int stage = 0, issued = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kcoord = kb_begin * kBlockK; kcoord < kb_end * kBlockK; kcoord += kBlockK) {
+        ok = wait_bounded(empty, phase ^ 1, ctx, kStProducerEmpty);
+        if (!ok) break;
+        if (elect_one()) {
+          SK_TRACE_EVENT(0, issued);
+          mbar_arrive_expect_tx(full, kStageTxBytes);
+          bulk_load_1d(dst_wp, wsrc, kWpBytes, full);
+          tma_load_2d(dst_x, &tmap_x, kcoord, m0, full);
         }
-        if (!ok) {
-          // Gave up: wait (bounded) until every copy this thread started has landed, so that none is in
-          // flight into this CTA's shared memory when the CTA exits.
-          const uint64_t t0 = globaltimer_ns();
-          const int first = issued > LSTAGES ? issued - LSTAGES : 0;
-          for (int i = first; i < issued; ++i) {
-            const int l = i % LSTAGES;
-            const uint32_t ph = (i / LSTAGES) & 1;
-            while (!mbar_try_wait(bar_ld_full(l), ph)) {
-              if (globaltimer_ns() - t0 > kWaitLimitNs) { atomicCAS(p.status, 0, kStDrain); break; }
-            }
+        __syncwarp();
+        wsrc += kWpBytes; ++issued;
+        if (++stage == LSTAGES) {
+          stage = 0; phase ^= 1;
+          dst_wp = smem_base + T::kOffWp; dst_x = smem_base + T::kOffX; full = bar_ld_full; empty = bar_ld_empty;
+        } else {
+          dst_wp += kWpBytes; dst_x += T::kXBytes; full += 8; empty += 8;
+        }
+      }
+      if (!ok) {
+        // Gave up: wait (bounded) until every copy this warp started has landed, so that none is in
+        // flight into this CTA's shared memory when the CTA exits.
+        const long long t0 = clock64();
+        const int first = issued > LSTAGES ? issued - LSTAGES : 0;
+        for (int i = first; i < issued; ++i) {
+          const int l = i % LSTAGES;
+          const uint32_t ph = (i / LSTAGES) & 1;
+          while (!mbar_try_wait(bar_ld_full + 8 * l, ph)) {
+            if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(p.status, 0, kStDrain); break; }
           }
         }
       }
       __syncwarp();
     } else if (warp == kMmaWarp) {
-      // ============================================================ MMA issuer
-      if (lane == 0) {
-        constexpr uint32_t idesc = make_idesc_i8(kTileN, BLOCK_M, /*a_signed=*/true, /*b_signed=*/true);
-        int it = 0;      // k-blocks consumed
-        int gcount = 0;  // groups started
-        bool ok = true;
-        for (int kb = kb_begin; kb < kb_end && ok; ++kb, ++it) {
-          const int l = it % LSTAGES, e = it % ESTAGES;
-          ok = wait_bounded(bar_ld_full(l), (it / LSTAGES) & 1, ctx, kStMmaLdFull) &&
-               wait_bounded(bar_ex_full(e), (it / ESTAGES) & 1, ctx, kStMmaExFull);
+      // ============================================================ MMA issuer (whole warp loops, one lane issues)
+      constexpr uint32_t idesc = make_idesc_i8(kTileN, BLOCK_M, /*a_signed=*/true, /*b_signed=*/true);
+      const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_base + T::kOffWx);
+      const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_base + T::kOffX);
+      int l = 0, e = 0, ab = 0;                 // load stage, expanded stage, accumulator buffer
+      uint32_t lph = 0, eph = 0, aph = 0;       // their phases
+      bool ok = true;
+      if (p.steps_per_group == 4) {
+        // one K block == one scale group: four MMAs and three commits per iteration, nothing else
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull) &&
+               wait_bounded(bar_ex_full + 8 * e, eph, ctx, kStMmaExFull) &&
+               wait_bounded(bar_acc_empty + 8 * ab, aph, ctx, kStMmaAccEmpty);
           if (!ok) break;
           tcgen05_fence_after_sync();
-          const uint64_t a_desc = make_kmajor_sw128_desc(smem_base + T::kOffWx + e * kWxBytes);
-          const uint64_t b_desc = make_kmajor_sw128_desc(smem_base + T::kOffX + l * T::kXBytes);
-#pragma unroll
+          if (elect_one()) {
+            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(e * (kWxBytes >> 4));
+            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(l * (T::kXBytes >> 4));
+            const uint32_t d = tmem_base + ab * BLOCK_M;
+            // +2 in the (address >> 4) field advances 32 bytes along K inside the 128-byte swizzle row
+            umma_i8(d, a_desc, b_desc, idesc, 1u);
+            umma_i8(d, a_desc + 2, b_desc + 2, idesc, 1u);
+            umma_i8(d, a_desc + 4, b_desc + 4, idesc, 1u);
+            umma_i8(d, a_desc + 6, b_desc + 6, idesc, 1u);
+            umma_commit(bar_acc_full + 8 * ab);
+            umma_commit(bar_ld_empty + 8 * l);
+            umma_commit(bar_ex_empty + 8 * e);
+            SK_TRACE_EVENT(2, kb - kb_begin);
+          }
+          __syncwarp();
+          if (++l == LSTAGES) { l = 0; lph ^= 1; }
+          if (++e == ESTAGES) { e = 0; eph ^= 1; }
+          if (++ab == ACC_BUFS) { ab = 0; aph ^= 1; }
+        }
+      } else {
+        // general group sizes (32, 64, 256, ...): track the position inside the group per 32-wide K step
+        int pos = 0;
+        for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
+          ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull) &&
+               wait_bounded(bar_ex_full + 8 * e, eph, ctx, kStMmaExFull);
+          if (!ok) break;
+          tcgen05_fence_after_sync();
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(e * (kWxBytes >> 4));
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(l * (T::kXBytes >> 4));
+#pragma unroll 1
           for (int s = 0; s < 4; ++s) {
             const int ks = kb * 4 + s;
             if (ks < ks_begin || ks >= ks_end) continue;
-            const int pos = ks % p.steps_per_group;
-            const int a = gcount & 1;
             if (pos == 0) {
-              // the epilogue pre-sets (and later re-sets) the buffer to the bias before releasing it
-              ok = wait_bounded(bar_acc_empty(a), (gcount >> 1) & 1, ctx, kStMmaAccEmpty);
+              ok = wait_bounded(bar_acc_empty + 8 * ab, aph, ctx, kStMmaAccEmpty);
               if (!ok) break;
               tcgen05_fence_after_sync();
             }
-            // advance 32 bytes along K inside the 128-byte swizzle row: +2 in the (address >> 4) field
-            umma_i8(tmem_base + a * BLOCK_M, a_desc + 2 * s, b_desc + 2 * s, idesc, 1u);
-            if (pos == p.steps_per_group - 1) {
-              umma_commit(bar_acc_full(a));
-              ++gcount;
+            const bool last = (pos == p.steps_per_group - 1);
+            if (elect_one()) {
+              umma_i8(tmem_base + ab * BLOCK_M, a_desc + 2 * s, b_desc + 2 * s, idesc, 1u);
+              if (last) umma_commit(bar_acc_full + 8 * ab);
+            }
+            __syncwarp();
+            if (last) {
+              pos = 0;
+              if (++ab == ACC_BUFS) { ab = 0; aph ^= 1; }
+            } else {
+              ++pos;
             }
           }
           if (!ok) break;
-          umma_commit(bar_ld_empty(l));
-          umma_commit(bar_ex_empty(e));
+          if (elect_one()) {
+            umma_commit(bar_ld_empty + 8 * l);
+            umma_commit(bar_ex_empty + 8 * e);
+          }
+          __syncwarp();
+          if (++l == LSTAGES) { l = 0; lph ^= 1; }
+          if (++e == ESTAGES) { e = 0; eph ^= 1; }
         }
       }
       __syncwarp();
     } else if (warp < kProducerWarp) {
-      // ============================================================ expanders (128 threads, one weight row each)
-      const int row = threadIdx.x - kExpWarp0 * 32;
+      // ============================================================ expanders (one or two weight rows per thread)
+      const int row0 = (threadIdx.x - kExpWarp0 * 32) * T::kRowsPerExpThread;
       const int zp = p.zero_point;
       const uint32_t lut = (static_cast<uint32_t>(0 - zp) & 0xffu) | ((static_cast<uint32_t>(1 - zp) & 0xffu) << 8) |
                            ((static_cast<uint32_t>(2 - zp) & 0xffu) << 16) | ((static_cast<uint32_t>(3 - zp) & 0xffu) << 24);
-      int it = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-        const int l = it % LSTAGES, e = it % ESTAGES;
-        if (!wait_bounded(bar_ld_full(l), (it / LSTAGES) & 1, ctx, kStExpanderFull)) break;
-        if (!wait_bounded(bar_ex_empty(e), ((it / ESTAGES) & 1) ^ 1, ctx, kStExpanderEmpty)) break;
-        const uint8_t* wp = smem + T::kOffWp + l * kWpBytes + row * 16;
-        uint8_t* wx = smem + T::kOffWx + e * kWxBytes + row * 128;
-        const int sw = row & 7;
+      int l = 0, e = 0;
+      uint32_t lph = 0, eph = 0;
+      // Row r of the expanded tile lives at r * 128; its 16-byte chunk c sits at chunk (c ^ (r & 7)).  The row base
+      // is 128-aligned, so  base + ((c ^ sw) << 4) == (base + (sw << 4)) ^ (c << 4): one XOR per store.
+      uint32_t wx_off[T::kRowsPerExpThread], wp_off[T::kRowsPerExpThread];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {     // codes 64h .. 64h+63 of this row: 16 bytes in, 64 bytes out
-          const uint4 q = *reinterpret_cast<const uint4*>(wp + h * 2048);
-          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+      for (int rr = 0; rr < T::kRowsPerExpThread; ++rr) {
+        const int row = row0 + rr;
+        wx_off[rr] = T::kOffWx + row * 128 + ((row & 7) << 4);
+        wp_off[rr] = T::kOffWp + row * 16;
+      }
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        // poll both barriers at once; the slow paths only run when a poll failed
+        const bool r1 = mbar_try_wait(bar_ld_full + 8 * l, lph);
+        const bool r2 = mbar_try_wait(bar_ex_empty + 8 * e, eph ^ 1);
+        if (!r1 && !wait_slow(bar_ld_full + 8 * l, lph, ctx.abort_flag, ctx.status, kStExpanderFull)) break;
+        if (!r2 && !wait_slow(bar_ex_empty + 8 * e, eph ^ 1, ctx.abort_flag, ctx.status, kStExpanderEmpty)) break;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(wx + (((4 * h + c) ^ sw) << 4)) = expand16(words[c], lut);
-          asm volatile("" ::: "memory");
+        for (int rr = 0; rr < T::kRowsPerExpThread; ++rr) {
+          const uint8_t* wp = smem + wp_off[rr] + l * kWpBytes;
+          const uint32_t wx = smem_base + wx_off[rr] + e * kWxBytes;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {     // codes 64h .. 64h+63 of this row: 16 bytes in, 64 bytes out
+            const uint4 q = *reinterpret_cast<const uint4*>(wp + h * 2048);
+            const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 o = expand16(words[c], lut);
+              st_shared_v4(wx ^ ((4 * h + c) << 4), o);
+            }
+          }
         }
-        mbar_arrive(bar_ld_empty(l));
         fence_proxy_async_smem();   // make the generic-proxy stores visible to the tensor core's async proxy
-        mbar_arrive(bar_ex_full(e));
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_ld_empty + 8 * l);
+          mbar_arrive(bar_ex_full + 8 * e);
+        }
+        if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, kb - kb_begin);
+        if (++l == LSTAGES) { l = 0; lph ^= 1; }
+        if (++e == ESTAGES) { e = 0; eph ^= 1; }
       }
     }
   } else {
@@ -316,54 +449,76 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
 #pragma unroll
     for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
 
-    // pre-set both accumulator buffers to the bias and hand them to the MMA issuer
+    // pre-set every accumulator buffer to the bias (once per tile) and hand them to the MMA issuer
 #pragma unroll
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < ACC_BUFS; ++a) {
 #pragma unroll
-      for (int c = 0; c < kNumChunks; ++c) {
-        if constexpr (kChunk == 32) tmem_st_fill_32x32(lane_addr + a * BLOCK_M + c * kChunk, bias);
-        else tmem_st_fill_32x16(lane_addr + a * BLOCK_M + c * kChunk, bias);
-      }
+      for (int c = 0; c < kNumChunks; ++c) tmem_fill_chunk<kChunk>(lane_addr + a * BLOCK_M + c * kChunk, bias);
     }
     tmem_st_wait();
     tcgen05_fence_before_sync();
-    mbar_arrive(bar_acc_empty(0));
-    mbar_arrive(bar_acc_empty(1));
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int a = 0; a < ACC_BUFS; ++a) mbar_arrive(bar_acc_empty + 8 * a);
+    }
 
-    float s_next = (n_ok && g_begin < g_end) ? __half2float(p.w_scale[static_cast<size_t>(g_begin) * p.N + n]) : 0.f;
-    float s_sum = 0.f;   // sum of scaled group scales since the last bias flush
-    int gc = 0;
-#pragma unroll 1
-    for (int g = g_begin; g < g_end; ++g, ++gc) {
-      const float s2 = s_next * kScaleUp;
-      if (g + 1 < g_end && n_ok) s_next = __half2float(p.w_scale[static_cast<size_t>(g + 1) * p.N + n]);
-      const int a = gc & 1;
-      if (!wait_bounded(bar_acc_full(a), (gc >> 1) & 1, ctx, kStEpilogueAccFull)) break;
-      tcgen05_fence_after_sync();
-      const uint32_t buf = lane_addr + a * BLOCK_M;
-      constexpr int kBufMask = T::kDoubleBuf ? 1 : 0;
-      uint32_t v[kBufMask + 1][kChunk];
-      if constexpr (T::kDoubleBuf) {
-        if constexpr (kChunk == 32) tmem_ld_32x32(buf, v[0]); else tmem_ld_32x16(buf, v[0]);
+    // group scales s_g .. s_{g+ACC_BUFS} in a register ring (loaded ACC_BUFS groups ahead; 0 past the end)
+    const __half* sp = p.w_scale + static_cast<size_t>(g_begin) * p.N + (n_ok ? n : 0);
+    auto load_scale = [&](int g) -> float {
+      return (n_ok && g < g_end) ? __half2float(__ldg(sp + static_cast<size_t>(g - g_begin) * p.N)) : 0.f;
+    };
+    float sr[ACC_BUFS + 1];
+#pragma unroll
+    for (int i = 0; i <= ACC_BUFS; ++i) sr[i] = load_scale(g_begin + i);
+    float s_sum = 0.f;   // sum of the coefficients since the last bias flush
+    int ab = 0, flush = 0;
+    uint32_t aph = 0;
+    // TMEM loads are software-pipelined across chunks AND groups: while chunk c is consumed the load of the
+    // next chunk -- or of the first chunk of the next group -- is already in flight.
+    constexpr bool kPipelined = false;   // cross-group prefetch costs more registers than the epilogue has
+    constexpr int kBufMask = T::kDoubleBuf ? 1 : 0;
+    uint32_t v[kBufMask + 1][kChunk];
+    bool epi_ok = true;
+    if constexpr (kPipelined) {
+      if (g_begin < g_end) {
+        epi_ok = wait_bounded(bar_acc_full, 0, ctx, kStEpilogueAccFull);
+        tcgen05_fence_after_sync();
+        tmem_ld_chunk<kChunk>(lane_addr, v[0]);
       }
+    }
+#pragma unroll 1
+    for (int g = g_begin; g < g_end && epi_ok; ++g) {
+      const float s2 = (sr[0] - sr[ACC_BUFS]) * kScaleUp;   // coefficient of this group's running sum
+#pragma unroll
+      for (int i = 0; i < ACC_BUFS; ++i) sr[i] = sr[i + 1];
+      sr[ACC_BUFS] = load_scale(g + ACC_BUFS + 1);
+      const uint32_t buf = lane_addr + ab * BLOCK_M;
+      if constexpr (!kPipelined) {
+        if (!wait_bounded(bar_acc_full + 8 * ab, aph, ctx, kStEpilogueAccFull)) break;
+        tcgen05_fence_after_sync();
+        if constexpr (T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf, v[0]);
+      }
+      int ab_next = ab + 1;
+      uint32_t aph_next = aph;
+      if (ab_next == ACC_BUFS) { ab_next = 0; aph_next ^= 1; }
 #pragma unroll
       for (int c = 0; c < kNumChunks; ++c) {
-        if constexpr (!T::kDoubleBuf) {
-          if constexpr (kChunk == 32) tmem_ld_32x32(buf + c * kChunk, v[0]); else tmem_ld_32x16(buf + c * kChunk, v[0]);
-        }
+        if constexpr (!T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf + c * kChunk, v[0]);
         tmem_ld_wait();
         if constexpr (T::kDoubleBuf) {
           if (c + 1 < kNumChunks) {
-            if constexpr (kChunk == 32) tmem_ld_32x32(buf + (c + 1) * kChunk, v[(c + 1) & 1]);
-            else tmem_ld_32x16(buf + (c + 1) * kChunk, v[(c + 1) & 1]);
+            tmem_ld_chunk<kChunk>(buf + (c + 1) * kChunk, v[(c + 1) & kBufMask]);
+          } else if (kPipelined && g + 1 < g_end) {
+            epi_ok = wait_bounded(bar_acc_full + 8 * ab_next, aph_next, ctx, kStEpilogueAccFull);
+            tcgen05_fence_after_sync();
+            tmem_ld_chunk<kChunk>(lane_addr + ab_next * BLOCK_M, v[0]);   // harmless if the wait gave up
           }
         }
-        if constexpr (kChunk == 32) tmem_st_fill_32x32(buf + c * kChunk, bias);
-        else tmem_st_fill_32x16(buf + c * kChunk, bias);
-        if (c == kNumChunks - 1) {   // buffer fully read and re-set: hand it back to the MMA issuer
-          tmem_st_wait();
+        if (c == kNumChunks - 1) {   // buffer fully read: hand it back to the MMA issuer (it keeps accumulating)
           tcgen05_fence_before_sync();
-          mbar_arrive(bar_acc_empty(a));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
         }
         if constexpr (DUMP) {
           if (n_ok) {
@@ -380,13 +535,15 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         for (int j = 0; j < kChunk; ++j)
           acc[c * kChunk + j] = fmaf(s2, __uint_as_float(v[c & kBufMask][j]), acc[c * kChunk + j]);
       }
+      if (threadIdx.x == 0) SK_TRACE_EVENT(3, g - g_begin);
       s_sum += s2;
-      if ((gc % kBiasFlushGroups) == kBiasFlushGroups - 1) {
+      if (++flush == kBiasFlushGroups) {
         const float corr = s_sum * bias_f;
 #pragma unroll
         for (int j = 0; j < kCols; ++j) acc[j] -= corr;
-        s_sum = 0.f;
+        s_sum = 0.f; flush = 0;
       }
+      ab = ab_next; aph = aph_next;
     }
     {
       const float corr = s_sum * bias_f;
@@ -403,6 +560,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       for (int j = threadIdx.x; j < BLOCK_M; j += T::kEpiThreads)
         xs_s[j] = (m0 + j < p.M) ? __ldg(p.x_scale + m0 + j) * kScaleDown : 0.f;
       named_barrier_sync(1, T::kEpiThreads);
+      if (threadIdx.x == 0) SK_TRACE_EVENT(4, 2);
       if (num_splits == 1) {
         uint16_t* st = reinterpret_cast<uint16_t*>(smem);   // [BLOCK_M][128] in the output dtype
 #pragma unroll
@@ -446,7 +604,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       const float kScaleDown = 5.62949953421312e14f;
       __syncwarp();
       cluster_sync_all();
-      if (warp < EPI_WGS * 4) {
+      if (warp < T::kEpiWarps) {
         const float* red = reinterpret_cast<const float*>(smem);
         const uint32_t my_rank = cluster_ctarank();
         const int row = threadIdx.x & 127;
@@ -474,6 +632,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
   // ---------------------------------------------------------------- teardown
   tcgen05_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) SK_TRACE_EVENT(4, 3);
   if (warp == kMmaWarp) {
     tcgen05_fence_after_sync();
     tmem_dealloc(tmem_base, T::kTmemCols);

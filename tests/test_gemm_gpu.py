@@ -217,7 +217,8 @@ def test_prefill_shape_against_checker_and_sampled_oracle():
     y = dp.gemm()
     dp.force(kernel=capi.KERNEL_CUDA_CORE)
     y_cc = dp.gemm()
-    assert (y.float() - y_cc.float()).abs().max().item() <= 2e-3
+    # two fp32 evaluation orders, each rounded to fp16 (ulp 2e-3 at |y| in [2, 4)): at most a few ulps apart
+    assert (y.float() - y_cc.float()).abs().max().item() <= 6e-3
     cols = np.arange(0, N, 509)
     y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp[cols], ws[:, cols])
     assert np.abs(to_np(y)[:, cols] - y_ref).max() <= TOL
