@@ -264,7 +264,7 @@ static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& 
                          int m_tiles, int split_k, cudaStream_t stream) {
   switch (token_tile) {
     // <tokens, epilogue warpgroups, expander warps, load stages, expanded stages, accumulator buffers>
-    case 16: return launch_umma<16, 1, 4, 8, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 16: return launch_umma<16, 1, 8, 8, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
     case 32: return launch_umma<32, 1, 4, 6, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
     case 64: return launch_umma<64, 1, 4, 6, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
     case 128: return launch_umma<128, 2, 4, 4, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);

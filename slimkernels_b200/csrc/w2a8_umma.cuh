@@ -94,7 +94,8 @@ struct KernelTraits {
   static constexpr int kWarps = ((kEpiWarps + EXP_WARPS + 2 + 3) / 4) * 4;   // whole warpgroups
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kEpiThreads = EPI_WGS * 128;
-  static constexpr int kRowsPerExpThread = 128 / (EXP_WARPS * 32);
+  static constexpr int kExpThreads = EXP_WARPS * 32;
+  static constexpr int kRowsPerExpThread = EXP_WARPS == 2 ? 2 : 1;   // with 8 warps a thread expands half a row
   static constexpr int kColsPerWg = BLOCK_M / EPI_WGS;           // accumulators per epilogue thread
   static constexpr int kChunk = kColsPerWg >= 32 ? 32 : 16;      // TMEM columns per tcgen05.ld
   static constexpr int kNumChunks = kColsPerWg / kChunk;
@@ -113,7 +114,7 @@ struct KernelTraits {
   // (fp32 [BLOCK_M][128] for the split-K reduction, 16-bit [BLOCK_M][128] otherwise).
   static_assert(BLOCK_M * kTileN * 4 <= kOffBar, "output staging must fit in the operand ring");
   static_assert(kColsPerWg % kChunk == 0 && kNumChunks >= 1, "bad epilogue split");
-  static_assert(EXP_WARPS == 2 || EXP_WARPS == 4, "expander warps");
+  static_assert(EXP_WARPS == 2 || EXP_WARPS == 4 || EXP_WARPS == 8, "expander warps");
   static_assert((ACC_BUFS & (ACC_BUFS - 1)) == 0 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM");
   // Register budgets.  With two epilogue warpgroups the epilogue threads hold kColsPerWg accumulators plus two
   // sets of TMEM-load registers and take registers from the other warpgroup(s) with setmaxnreg.  The CTA's pool
@@ -137,6 +138,7 @@ struct KernelTraits {
   // already overlap each other's load latency).
   static constexpr bool kDoubleBuf = (kNumChunks > 1) && (kColsPerWg <= 64);
   static constexpr int kMinBlocks = (BLOCK_M <= 32) ? 2 : 1;
+  static_assert(kMinBlocks * kThreads <= 2048, "threads per SM");
 };
 
 struct WaitCtx {
@@ -385,7 +387,10 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       __syncwarp();
     } else if (warp < kProducerWarp) {
       // ============================================================ expanders (one or two weight rows per thread)
-      const int row0 = (threadIdx.x - kExpWarp0 * 32) * T::kRowsPerExpThread;
+      const int et = threadIdx.x - kExpWarp0 * 32;             // expander thread index
+      constexpr bool kHalfRows = (EXP_WARPS == 8);             // 8 warps: a thread expands half a row
+      const int row0 = kHalfRows ? (et >> 1) : et * T::kRowsPerExpThread;
+      const int half = kHalfRows ? (et & 1) : 0;
       const int zp = p.zero_point;
       const uint32_t lut = (static_cast<uint32_t>(0 - zp) & 0xffu) | ((static_cast<uint32_t>(1 - zp) & 0xffu) << 8) |
                            ((static_cast<uint32_t>(2 - zp) & 0xffu) << 16) | ((static_cast<uint32_t>(3 - zp) & 0xffu) << 24);
@@ -398,7 +403,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       for (int rr = 0; rr < T::kRowsPerExpThread; ++rr) {
         const int row = row0 + rr;
         wx_off[rr] = T::kOffWx + row * 128 + ((row & 7) << 4);
-        wp_off[rr] = T::kOffWp + row * 16;
+        wp_off[rr] = T::kOffWp + row * 16 + half * 2048;
       }
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         // poll both barriers at once; the slow paths only run when a poll failed
@@ -410,15 +415,19 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         for (int rr = 0; rr < T::kRowsPerExpThread; ++rr) {
           const uint8_t* wp = smem + wp_off[rr] + l * kWpBytes;
           const uint32_t wx = smem_base + wx_off[rr] + e * kWxBytes;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {     // codes 64h .. 64h+63 of this row: 16 bytes in, 64 bytes out
-            const uint4 q = *reinterpret_cast<const uint4*>(wp + h * 2048);
+          if constexpr (kHalfRows) {
+            // 16 bytes in (codes 64 half .. +63 of this row), 64 bytes out
+            const uint4 q = *reinterpret_cast<const uint4*>(wp);
             const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const uint4 o = expand16(words[c], lut);
-              st_shared_v4(wx ^ ((4 * h + c) << 4), o);
-            }
+            for (int c = 0; c < 4; ++c) st_shared_v4(wx ^ ((4 * half + c) << 4), expand16(words[c], lut));
+          } else {
+            // 2 x 16 bytes in (codes 0..63 and 64..127 of this row), 128 bytes out
+            const uint4 q0 = *reinterpret_cast<const uint4*>(wp);
+            const uint4 q1 = *reinterpret_cast<const uint4*>(wp + 2048);
+            const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) st_shared_v4(wx ^ (c << 4), expand16(words[c], lut));
           }
         }
         fence_proxy_async_smem();   // make the generic-proxy stores visible to the tensor core's async proxy
@@ -463,14 +472,19 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       for (int a = 0; a < ACC_BUFS; ++a) mbar_arrive(bar_acc_empty + 8 * a);
     }
 
-    // group scales s_g .. s_{g+ACC_BUFS} in a register ring (loaded ACC_BUFS groups ahead; 0 past the end)
-    const __half* sp = p.w_scale + static_cast<size_t>(g_begin) * p.N + (n_ok ? n : 0);
-    auto load_scale = [&](int g) -> float {
-      return (n_ok && g < g_end) ? __half2float(__ldg(sp + static_cast<size_t>(g - g_begin) * p.N)) : 0.f;
+    // group scales s_g .. s_{g+ACC_BUFS} in a register ring, loaded ACC_BUFS groups ahead (0 past the end).
+    // The ring keeps the raw fp16 bits: converting at load time would stall on the global load right away.
+    const unsigned short* sp =
+        reinterpret_cast<const unsigned short*>(p.w_scale) + static_cast<size_t>(g_begin) * p.N + (n_ok ? n : 0);
+    int g_load = g_begin;                       // next group whose scale is fetched
+    auto load_scale = [&]() -> unsigned short {
+      const unsigned short r = (n_ok && g_load < g_end) ? __ldg(sp) : static_cast<unsigned short>(0);
+      sp += p.N; ++g_load;
+      return r;
     };
-    float sr[ACC_BUFS + 1];
+    unsigned short sr[ACC_BUFS + 1];
 #pragma unroll
-    for (int i = 0; i <= ACC_BUFS; ++i) sr[i] = load_scale(g_begin + i);
+    for (int i = 0; i <= ACC_BUFS; ++i) sr[i] = load_scale();
     float s_sum = 0.f;   // sum of the coefficients since the last bias flush
     int ab = 0, flush = 0;
     uint32_t aph = 0;
@@ -489,13 +503,16 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
     }
 #pragma unroll 1
     for (int g = g_begin; g < g_end && epi_ok; ++g) {
-      const float s2 = (sr[0] - sr[ACC_BUFS]) * kScaleUp;   // coefficient of this group's running sum
+      // coefficient of this group's running sum
+      const float s2 = (__half2float(__ushort_as_half(sr[0])) - __half2float(__ushort_as_half(sr[ACC_BUFS]))) * kScaleUp;
 #pragma unroll
       for (int i = 0; i < ACC_BUFS; ++i) sr[i] = sr[i + 1];
-      sr[ACC_BUFS] = load_scale(g + ACC_BUFS + 1);
+      sr[ACC_BUFS] = load_scale();
       const uint32_t buf = lane_addr + ab * BLOCK_M;
       if constexpr (!kPipelined) {
+        if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 0);
         if (!wait_bounded(bar_acc_full + 8 * ab, aph, ctx, kStEpilogueAccFull)) break;
+        if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 1);
         tcgen05_fence_after_sync();
         if constexpr (T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf, v[0]);
       }
@@ -506,6 +523,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       for (int c = 0; c < kNumChunks; ++c) {
         if constexpr (!T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf + c * kChunk, v[0]);
         tmem_ld_wait();
+        if (threadIdx.x == 0 && c < 4) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 2 + c);
         if constexpr (T::kDoubleBuf) {
           if (c + 1 < kNumChunks) {
             tmem_ld_chunk<kChunk>(buf + (c + 1) * kChunk, v[(c + 1) & kBufMask]);
@@ -611,13 +629,18 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         const int wg = warp >> 2;
         const int n = n0 + row;
         uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
-        // token rows are dealt round-robin to (cluster rank, epilogue warpgroup)
+        // token rows are dealt round-robin to (cluster rank, epilogue warpgroup); every remote load of a row
+        // is issued before the first is consumed, and the sum runs in rank order (deterministic)
         for (int j = static_cast<int>(my_rank) * EPI_WGS + wg; j < BLOCK_M; j += num_splits * EPI_WGS) {
           const int m = m0 + j;
           if (m >= p.M) break;
           const uint32_t local = smem_u32(red + j * kTileN + row);
+          float part[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) part[r] = (r < num_splits) ? ld_dsmem_f32(map_to_cta(local, r)) : 0.f;
           float sum = 0.f;
-          for (int r = 0; r < num_splits; ++r) sum += ld_dsmem_f32(map_to_cta(local, r));
+#pragma unroll
+          for (int r = 0; r < 8; ++r) sum += part[r];
           const float y = sum * (__ldg(p.x_scale + m) * kScaleDown);
           if (n < p.N)
             outp[static_cast<size_t>(m) * p.ld_out + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
