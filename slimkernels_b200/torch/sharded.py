@@ -31,7 +31,7 @@ class ShardedW2A8Gemm:
     """Holds this rank's weight slice; ``forward`` returns the full [M, N] output on every rank."""
 
     def __init__(self, w_packed_local, w_scale_local, N_total: int, group=None, group_size=128, zero_point=1,
-                 out_dtype=torch.float16):
+                 out_dtype=torch.float16, plan_factory=W2A8Plan):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -39,8 +39,10 @@ class ShardedW2A8Gemm:
         self.N_local = w_packed_local.shape[0]
         assert self.N_local * self.world == N_total
         self.out_dtype = out_dtype
-        self.plan = W2A8Plan(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
-                             out_dtype=out_dtype)
+        # plan_factory exists so that the sharding / gathering logic can be exercised on CPU ranks (gloo) with a
+        # stand-in for the device GEMM; the product default is the CUDA plan and nothing else
+        self.plan = plan_factory(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
+                                 out_dtype=out_dtype)
         self._bufs = {}
 
     def _buffers(self, M, device):
@@ -62,7 +64,7 @@ class ShardedW2A8Gemm:
         self.plan.gemm(x_q, x_scale, out=local)
         if self.world == 1:
             return local
-        dist.all_gather_into_tensor(gathered, local, group=self.group)
+        dist.all_gather_into_tensor(gathered.view(self.world * M, self.N_local), local, group=self.group)
         # [R, M, N/R] -> [M, R, N/R] == [M, N]
         full.view(M, self.world, self.N_local).copy_(gathered.permute(1, 0, 2))
         return full

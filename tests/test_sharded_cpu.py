@@ -1,0 +1,81 @@
+"""N-sharded execution on CPU ranks (gloo, world size 2): slicing, all-gather and the [R, M, N/R] -> [M, N]
+re-ordering, with the device GEMM replaced by the CPU oracle.  The CUDA GEMM itself is covered by the gpu tests."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+class OraclePlan:
+    """Stand-in for W2A8Plan on CPU ranks: same call surface, computed by the oracle."""
+
+    def __init__(self, w_packed, w_scale, group_size=128, zero_point=1, out_dtype=torch.float16):
+        self.w_packed, self.w_scale, self.G, self.zp, self.dt = w_packed.numpy(), w_scale.numpy(), group_size, zero_point, out_dtype
+
+    def gemm(self, x_q, x_scale, out=None):
+        from oracle import w2a8_oracle as O
+        y = torch.from_numpy(O.w2a8_gemm_int_path(x_q.numpy(), x_scale.numpy(), self.w_packed, self.w_scale, self.G, self.zp))
+        out.copy_(y.to(self.dt))
+        return out
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import w2a8_oracle as O
+        from slimkernels_b200 import workloads as W
+        from slimkernels_b200.torch.sharded import ShardedW2A8Gemm, shard_bounds, shard_weight
+        M, N, K, G = 6, 512, 256, 128
+        x_q, x_scale, w_packed, w_scale = W.make_problem(M, N, K, G, seed=0)
+        lo, hi = shard_bounds(N, world, rank)
+        assert (lo, hi) == (rank * N // world, (rank + 1) * N // world)
+        wl, sl = shard_weight(torch.from_numpy(w_packed), torch.from_numpy(w_scale), world, rank)
+        assert wl.is_contiguous() and sl.is_contiguous() and wl.shape == (N // world, K // 4) and sl.shape == (K // G, N // world)
+        op = ShardedW2A8Gemm(wl, sl, N, group_size=G, plan_factory=OraclePlan)
+        y = op(torch.from_numpy(x_q), torch.from_numpy(x_scale))
+        ref = O.w2a8_gemm_int_path(x_q, x_scale, w_packed, w_scale, G).astype(np.float16)
+        q.put((rank, bool(np.array_equal(y.numpy(), ref)), tuple(y.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_shard_and_gather_on_cpu():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=60) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in results) == [0, 1]
+    for _, equal, shape in results:
+        assert equal and shape == (6, 512)
+
+
+def test_shard_bounds_rejects_ragged_split():
+    from slimkernels_b200.torch.sharded import shard_bounds
+    with pytest.raises(ValueError):
+        shard_bounds(4096 + 128, 8, 0)
+    assert shard_bounds(57344, 8, 7) == (50176, 57344)
+    assert shard_bounds(8192, 8, 3) == (3072, 4096)
