@@ -178,7 +178,8 @@ def run_reference_arm(args):
 def config_dict(n_gpus):
     return {"workload": f"{WORKLOAD['name']}: M={WORKLOAD['M']} N={WORKLOAD['N']} K={WORKLOAD['K']} G={WORKLOAD['G']} "
                         f"int8 x 2-bit -> fp16, seed 0 synthetic (benchmark config 3, gate+up)",
-            "parallelism": f"N-sharded x{n_gpus} + NCCL all-gather" if n_gpus > 1 else "single GPU",
+            "parallelism": (f"N-sharded x{n_gpus}, output all-gathered (peer stores in the GEMM epilogue over NVLink; "
+                            f"--nccl-gather selects NCCL all_gather after the GEMM)") if n_gpus > 1 else "single GPU",
             "l2": "inputs larger than L2 (weights 117 MB + activations 34 MB + output 470 MB per step)"}
 
 
@@ -317,7 +318,8 @@ def run_ours(args):
     h_x = torch.from_numpy(x_q_np).pin_memory()
     h_xs = torch.from_numpy(x_scale_np).pin_memory()
     d_x, d_xs = h_x.to(dev), h_xs.to(dev)
-    op = ShardedW2A8Gemm(wp, ws, N, group_size=G)
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    op = ShardedW2A8Gemm(wp, ws, N, group_size=G, fused=(world > 1 and not args.nccl_gather))
     h_out = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
     stream = torch.cuda.current_stream(dev)
 
@@ -413,6 +415,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweeps", action="store_true", help="skip the decode / prefill sweeps at N=1")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="N>1: exchange the output with NCCL all-gather after the GEMM instead of peer stores in its epilogue")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

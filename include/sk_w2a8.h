@@ -87,6 +87,14 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value);
 int sk_w2a8_gemm(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
                  void* out, int64_t ld_out, sk_stream_t stream);
 
+/* The same GEMM, written to several destinations at once: the [M, N] result lands at column `col_offset` of each
+ * of the n_outs (1..8) row-major buffers outs[i] of leading dimension ld_out.  outs[0] is a local buffer, the
+ * others may be peer-mapped buffers of other GPUs (CUDA IPC / symmetric memory): the kernel's epilogue stores
+ * every tile to all of them with plain global stores, so an N-sharded all-gather of the output overlaps the
+ * GEMM.  The caller synchronises the ranks afterwards.  No counterpart in the reference (single-GPU only). */
+int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
+                         void* const* outs, int n_outs, int64_t ld_out, int64_t col_offset, sk_stream_t stream);
+
 /* Same contraction, but stores the exact per-group integer partial sums
  * partials[g, m, n] (int32, [K/G, M, N] contiguous) instead of the scaled output. */
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,

@@ -297,7 +297,8 @@ static int get_x_map(sk_w2a8_plan* plan, const int8_t* x_q, long long M, long lo
 }
 
 static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long long ld_x, const float* x_scale,
-                    void* out, long long ld_out, int32_t* partials, cudaStream_t stream) {
+                    void* out, long long ld_out, int32_t* partials, cudaStream_t stream,
+                    void* const* extra_outs = nullptr, int n_extra = 0) {
   if (!plan || !x_q) return SK_ERR_NULL_POINTER;
   if (!partials && (!x_scale || !out)) return SK_ERR_NULL_POINTER;
   if (M <= 0 || M > 0x7fffffffLL / 2) return SK_ERR_BAD_SHAPE;
@@ -321,7 +322,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
   }
   int rc = SK_OK;
   if (ch.kernel == 2) {
-    if (!plan->w_rowmajor) rc = SK_ERR_UNAVAILABLE;
+    if (!plan->w_rowmajor || n_extra > 0) rc = SK_ERR_UNAVAILABLE;
     else {
       dim3 block(32, 8, 1);
       dim3 grid(static_cast<unsigned>((plan->N + 31) / 32), static_cast<unsigned>((M + 7) / 8), 1);
@@ -341,6 +342,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.w_scale = plan->w_scale;
       prm.x_scale = x_scale;
       prm.out = out;
+      prm.n_extra = n_extra;
+      for (int i = 0; i < 7; ++i) prm.out_extra[i] = i < n_extra ? extra_outs[i] : nullptr;
       prm.partials = partials;
       prm.status = plan->status;
       prm.ld_out = ld_out;
@@ -545,6 +548,22 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
 int sk_w2a8_gemm(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale, void* out,
                  int64_t ld_out, sk_stream_t stream) {
   return sk::run_gemm(plan, M, x_q, ld_x, x_scale, out, ld_out, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
+                         void* const* outs, int n_outs, int64_t ld_out, int64_t col_offset, sk_stream_t stream) {
+  if (!outs) return SK_ERR_NULL_POINTER;
+  if (n_outs < 1 || n_outs > 8) return SK_ERR_BAD_ARGUMENT;
+  if (!plan) return SK_ERR_NULL_POINTER;
+  if (col_offset < 0 || col_offset + plan->N > ld_out) return SK_ERR_BAD_SHAPE;
+  const size_t esz = 2;   // half and bfloat16
+  void* shifted[8];
+  for (int i = 0; i < n_outs; ++i) {
+    if (!outs[i]) return SK_ERR_NULL_POINTER;
+    shifted[i] = static_cast<char*>(outs[i]) + static_cast<size_t>(col_offset) * esz;
+  }
+  return sk::run_gemm(plan, M, x_q, ld_x, x_scale, shifted[0], ld_out, nullptr, static_cast<cudaStream_t>(stream),
+                      shifted + 1, n_outs - 1);
 }
 
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, int32_t* partials,

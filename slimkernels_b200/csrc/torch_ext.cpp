@@ -68,6 +68,24 @@ void gemm_out(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, 
         "w2a8_gemm");
 }
 
+// outs: raw device pointers (this rank's buffer first, then peer-mapped buffers) of [M, ld_out] row-major buffers
+void gemm_scatter(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, std::vector<int64_t> out_ptrs,
+                  int64_t ld_out, int64_t col_offset, int64_t K) {
+  check_x(x_q, K);
+  const int64_t M = x_q.size(0);
+  TORCH_CHECK(x_scale.is_cuda() && x_scale.scalar_type() == at::kFloat && x_scale.is_contiguous() &&
+                  x_scale.numel() == M, "x_scale must be contiguous float32 [M]");
+  TORCH_CHECK(!out_ptrs.empty() && out_ptrs.size() <= 8, "1..8 destinations");
+  if (M == 0) return;
+  std::vector<void*> ptrs;
+  for (int64_t v : out_ptrs) ptrs.push_back(reinterpret_cast<void*>(static_cast<intptr_t>(v)));
+  c10::cuda::CUDAGuard guard(x_q.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check(sk_w2a8_gemm_scatter(as_plan(handle), M, x_q.data_ptr<int8_t>(), x_q.stride(0), x_scale.data_ptr<float>(),
+                             ptrs.data(), static_cast<int>(ptrs.size()), ld_out, col_offset, stream.stream()),
+        "w2a8_gemm_scatter");
+}
+
 at::Tensor gemm(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, int64_t N, int64_t K, bool bf16_out) {
   at::Tensor out = at::empty({x_q.size(0), N}, x_q.options().dtype(bf16_out ? at::kBFloat16 : at::kHalf));
   gemm_out(handle, x_q, x_scale, out, K);
@@ -123,6 +141,7 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_set_option(int plan, int key, int value) -> ()", &plan_set_option);
   m.def("w2a8_plan_gemm(int plan, Tensor x_q, Tensor x_scale, int N, int K, bool bf16_out) -> Tensor", &gemm);
   m.def("w2a8_plan_gemm_out(int plan, Tensor x_q, Tensor x_scale, Tensor(a!) out, int K) -> ()", &gemm_out);
+  m.def("w2a8_plan_gemm_scatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int ld_out, int col_offset, int K) -> ()", &gemm_scatter);
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
   m.def("w2a8_repack(Tensor w_packed) -> Tensor", &repack);

@@ -74,6 +74,8 @@ struct GemmParams {
   const __half* w_scale;      // [groups, N]
   const float* x_scale;       // [M]
   void* out;                  // [M, ld_out] half or bf16
+  void* out_extra[7];         // further destinations of the same tile (peer GPUs' buffers), same ld_out
+  int n_extra;                // how many of them are used
   int32_t* partials;          // [groups, M, N] (debug mode) or nullptr
   int* status;                // device status word
   long long ld_out;
@@ -589,23 +591,27 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
                                                      : __half_as_ushort(__float2half_rn(y));
         }
         named_barrier_sync(1, T::kEpiThreads);
-        uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
-        const bool vec_ok = (n0 + kTileN <= p.N) && (p.ld_out % 8 == 0) &&
-                            ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-        if (vec_ok) {
-          // 16 threads x 16 bytes cover one 256-byte row of the tile
-          for (int idx = threadIdx.x; idx < BLOCK_M * 16; idx += T::kEpiThreads) {
-            const int j = idx >> 4, ch = idx & 15;
-            const int m = m0 + j;
-            if (m < p.M)
-              *reinterpret_cast<uint4*>(outp + static_cast<size_t>(m) * p.ld_out + n0 + ch * 8) =
-                  *reinterpret_cast<const uint4*>(st + j * kTileN + ch * 8);
-          }
-        } else {
-          for (int idx = threadIdx.x; idx < BLOCK_M * kTileN; idx += T::kEpiThreads) {
-            const int j = idx >> 7, r = idx & 127;
-            const int m = m0 + j;
-            if (m < p.M && n0 + r < p.N) outp[static_cast<size_t>(m) * p.ld_out + n0 + r] = st[j * kTileN + r];
+        // destination 0 is this GPU's buffer; the others are peer-mapped buffers of the other ranks (plain
+        // stores over NVLink, so the all-gather of the output overlaps the GEMM tile by tile)
+        for (int d = 0; d <= p.n_extra; ++d) {
+          uint16_t* outp = reinterpret_cast<uint16_t*>(d == 0 ? p.out : p.out_extra[d - 1]);
+          const bool vec_ok = (n0 + kTileN <= p.N) && (p.ld_out % 8 == 0) &&
+                              ((reinterpret_cast<uintptr_t>(outp) & 15) == 0);
+          if (vec_ok) {
+            // 16 threads x 16 bytes cover one 256-byte row of the tile
+            for (int idx = threadIdx.x; idx < BLOCK_M * 16; idx += T::kEpiThreads) {
+              const int j = idx >> 4, ch = idx & 15;
+              const int m = m0 + j;
+              if (m < p.M)
+                *reinterpret_cast<uint4*>(outp + static_cast<size_t>(m) * p.ld_out + n0 + ch * 8) =
+                    *reinterpret_cast<const uint4*>(st + j * kTileN + ch * 8);
+            }
+          } else {
+            for (int idx = threadIdx.x; idx < BLOCK_M * kTileN; idx += T::kEpiThreads) {
+              const int j = idx >> 7, r = idx & 127;
+              const int m = m0 + j;
+              if (m < p.M && n0 + r < p.N) outp[static_cast<size_t>(m) * p.ld_out + n0 + r] = st[j * kTileN + r];
+            }
           }
         }
       } else {
@@ -642,9 +648,13 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
 #pragma unroll
           for (int r = 0; r < 8; ++r) sum += part[r];
           const float y = sum * (__ldg(p.x_scale + m) * kScaleDown);
-          if (n < p.N)
-            outp[static_cast<size_t>(m) * p.ld_out + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
-                                                                     : __half_as_ushort(__float2half_rn(y));
+          if (n < p.N) {
+            const uint16_t bits = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
+                                             : __half_as_ushort(__float2half_rn(y));
+            outp[static_cast<size_t>(m) * p.ld_out + n] = bits;
+            for (int d = 0; d < p.n_extra; ++d)
+              reinterpret_cast<uint16_t*>(p.out_extra[d])[static_cast<size_t>(m) * p.ld_out + n] = bits;
+          }
         }
       }
       __syncwarp();

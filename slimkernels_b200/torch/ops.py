@@ -60,6 +60,11 @@ class W2A8Plan:
         torch.ops.slimkernels.w2a8_plan_gemm_out(self._h, x_q, x_scale, out, self.K)
         return out
 
+    def gemm_scatter(self, x_q, x_scale, out_ptrs, ld_out: int, col_offset: int) -> None:
+        """Writes the [M, N] result at column `col_offset` of every [M, ld_out] buffer in `out_ptrs` (raw device
+        pointers: this GPU's buffer first, then peer-mapped buffers of the other ranks)."""
+        torch.ops.slimkernels.w2a8_plan_gemm_scatter(self._h, x_q, x_scale, list(out_ptrs), ld_out, col_offset, self.K)
+
     def partials(self, x_q):
         return torch.ops.slimkernels.w2a8_plan_partials(self._h, x_q, self.N, self.K, self.group_size)
 

@@ -7,6 +7,8 @@ The reference has no multi-GPU code; this is the one parallel strategy the W2A8 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -31,7 +33,7 @@ class ShardedW2A8Gemm:
     """Holds this rank's weight slice; ``forward`` returns the full [M, N] output on every rank."""
 
     def __init__(self, w_packed_local, w_scale_local, N_total: int, group=None, group_size=128, zero_point=1,
-                 out_dtype=torch.float16, plan_factory=W2A8Plan):
+                 out_dtype=torch.float16, plan_factory=W2A8Plan, fused=False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -44,6 +46,8 @@ class ShardedW2A8Gemm:
         self.plan = plan_factory(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
                                  out_dtype=out_dtype)
         self._bufs = {}
+        self.fused = bool(fused) and self.world > 1
+        self._symm = {}
 
     def _buffers(self, M, device):
         key = (M, device)
@@ -58,7 +62,30 @@ class ShardedW2A8Gemm:
         local, _, _ = self._buffers(x_q.shape[0], x_q.device)
         return self.plan.gemm(x_q, x_scale, out=local)
 
+    def _symmetric(self, M, device):
+        """[M, N_total] output buffer in symmetric memory + the peers' pointers to it (this rank's first, then the
+        others in ring order so that the ranks do not all write to the same peer at the same time)."""
+        key = (M, device)
+        if key not in self._symm:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
+            import torch.distributed._symmetric_memory as symm_mem
+            group = self.group if self.group is not None else dist.group.WORLD
+            buf = symm_mem.empty((M, self.N_total), dtype=self.out_dtype, device=device)
+            hdl = symm_mem.rendezvous(buf, group)
+            ptrs = [int(hdl.buffer_ptrs[(self.rank + i) % self.world]) for i in range(self.world)]
+            self._symm[key] = (buf, hdl, ptrs)
+        return self._symm[key]
+
+    def forward_fused(self, x_q, x_scale):
+        M = x_q.shape[0]
+        buf, hdl, ptrs = self._symmetric(M, x_q.device)
+        self.plan.gemm_scatter(x_q, x_scale, ptrs, self.N_total, self.rank * self.N_local)
+        hdl.barrier()          # every rank's tiles have landed everywhere (stream-ordered device barrier)
+        return buf
+
     def forward(self, x_q, x_scale):
+        if self.fused:
+            return self.forward_fused(x_q, x_scale)
         M = x_q.shape[0]
         local, gathered, full = self._buffers(M, x_q.device)
         self.plan.gemm(x_q, x_scale, out=local)

@@ -20,10 +20,11 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, fused=False):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -34,7 +35,7 @@ def _worker(rank, world, port, q):
         M, N, K, G = 300, 1024, 512, 128
         x_q, x_scale, w_packed, w_scale = W.make_problem(M, N, K, G, seed=0)
         wl, sl = shard_weight(torch.from_numpy(w_packed).to(dev), torch.from_numpy(w_scale).to(dev), world, rank)
-        op = ShardedW2A8Gemm(wl, sl, N, group_size=G)
+        op = ShardedW2A8Gemm(wl, sl, N, group_size=G, fused=fused)
         y = op(torch.from_numpy(x_q).to(dev), torch.from_numpy(x_scale).to(dev))
         torch.cuda.synchronize(dev)
         ref = O.w2a8_gemm_dequant_path(x_q, x_scale, w_packed, w_scale, G)
@@ -44,13 +45,14 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_shard_and_allgather(built_libs):
+@pytest.mark.parametrize("fused", [False, True], ids=["nccl_allgather", "peer_store_epilogue"])
+def test_two_gpu_shard_and_allgather(built_libs, fused):
     import torch.multiprocessing as mp
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, fused)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
