@@ -100,6 +100,25 @@ int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,
                                 int32_t* partials, sk_stream_t stream);
 
+/* -------- activation side of the Llama MLP block -----------------------------------------------------
+ * The reference has no activation quantiser (its prototype is fed ready-made e4m3 tensors,
+ * wgmma_sm90_W2A8.cu:541-552).  Definition used here, per token row:
+ *   s = max|x| / 127 (1.0 for an all-zero row),  q = clamp(round_half_even(x / s), -127, 127).
+ * x fp16 [M, ld_x] -> x_q int8 [M, ld_q], x_scale fp32 [M].  K % 8 == 0, rows 16-byte aligned. */
+int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int64_t K, int8_t* x_q, int64_t ld_q,
+                                float* x_scale, sk_stream_t stream);
+/* gate_up fp16 [M, ld_gu] (gate = columns [0, I), up = [I, 2I)) -> h = SiLU(gate) * up in fp32, quantised as
+ * above to h_q int8 [M, ld_q], h_scale fp32 [M].  I % 8 == 0, I <= 51200. */
+int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M, int64_t I, int8_t* h_q,
+                              int64_t ld_q, float* h_scale, sk_stream_t stream);
+/* The whole block: quantise x, W2A8 GEMM with the fused gate+up weight ([2I, hidden] packed, gate rows first),
+ * SiLU*up + re-quantise, W2A8 GEMM with the down weight ([hidden, I]).  The intermediates live in a
+ * caller-provided device workspace of sk_w2a8_mlp_workspace_bytes(...) bytes (256-byte aligned); nothing is
+ * allocated.  gate_up's plan must produce fp16.  Four launches on `stream`, no synchronisation. */
+int64_t sk_w2a8_mlp_workspace_bytes(const sk_w2a8_plan* gate_up, const sk_w2a8_plan* down, int64_t M);
+int sk_w2a8_mlp_forward(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, const void* x_f16, int64_t ld_x,
+                        void* out, int64_t ld_out, void* workspace, int64_t workspace_bytes, sk_stream_t stream);
+
 /* -------- diagnostics -----------------------------------------------------------------------------*/
 /* Synchronously reads (and clears) the plan's device status word: 0, or a code naming the wait that
  * expired inside the kernel (role * 16 + barrier kind).  Non-zero maps to SK_ERR_DEVICE_TIMEOUT. */

@@ -10,6 +10,7 @@
 #include <new>
 #include <vector>
 
+#include "activation.cuh"
 #include "w2a8_umma.cuh"
 
 namespace sk {
@@ -597,6 +598,107 @@ int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* sp
   if (ctas) *ctas = static_cast<int>(plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile) * c.split_k);
   if (kernel_kind) *kernel_kind = c.kernel;
   return SK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- activation side
+int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int64_t K, int8_t* x_q, int64_t ld_q,
+                                float* x_scale, sk_stream_t stream) {
+  if (!x_f16 || !x_q || !x_scale) return SK_ERR_NULL_POINTER;
+  if (M <= 0 || K <= 0 || (K % 8) != 0 || ld_x < K || ld_q < K || M > 0x7fffffffLL) return SK_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x_f16) & 15) || (ld_x % 8) || (reinterpret_cast<uintptr_t>(x_q) & 7) || (ld_q % 8))
+    return SK_ERR_BAD_ALIGNMENT;
+  auto st = static_cast<cudaStream_t>(stream);
+  const __half* x = static_cast<const __half*>(x_f16);
+  const dim3 grid(static_cast<unsigned>(M));
+  if (K <= 8 * sk::kActThreads * 2)
+    sk::quantize_activation_kernel<2><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
+  else
+    sk::quantize_activation_kernel<8><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
+  if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
+  return SK_OK;
+}
+
+int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M, int64_t I, int8_t* h_q, int64_t ld_q,
+                              float* h_scale, sk_stream_t stream) {
+  if (!gate_up_f16 || !h_q || !h_scale) return SK_ERR_NULL_POINTER;
+  if (M <= 0 || I <= 0 || (I % 8) != 0 || ld_gu < 2 * I || ld_q < I || M > 0x7fffffffLL) return SK_ERR_BAD_SHAPE;
+  if (4 * I > 200 * 1024) return SK_ERR_BAD_SHAPE;   // the fp32 row is kept in shared memory
+  if ((reinterpret_cast<uintptr_t>(gate_up_f16) & 15) || (ld_gu % 8) || (reinterpret_cast<uintptr_t>(h_q) & 7) || (ld_q % 8))
+    return SK_ERR_BAD_ALIGNMENT;
+  const int smem = static_cast<int>(4 * I);
+  if (smem > 48 * 1024) {
+    // per device, once: allow the larger dynamic shared memory window
+    static bool configured[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SK_ERR_CUDA;
+    if (dev < 64 && !configured[dev]) {
+      if (cudaFuncSetAttribute(sk::silu_mul_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+          cudaSuccess)
+        return SK_ERR_CUDA;
+      configured[dev] = true;
+    }
+  }
+  sk::silu_mul_quantize_kernel<<<static_cast<unsigned>(M), sk::kActThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(gate_up_f16), ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
+  if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
+  return SK_OK;
+}
+
+// workspace layout of the MLP block (all offsets 256-byte aligned)
+namespace {
+struct MlpLayout {
+  size_t x_q, x_scale, gate_up, h_q, h_scale, total;
+};
+inline size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+inline MlpLayout mlp_layout(int64_t M, int64_t hidden, int64_t inter) {
+  MlpLayout l;
+  size_t o = 0;
+  l.x_q = o;     o = up256(o + static_cast<size_t>(M) * hidden);
+  l.x_scale = o; o = up256(o + static_cast<size_t>(M) * 4);
+  l.gate_up = o; o = up256(o + static_cast<size_t>(M) * 2 * inter * 2);
+  l.h_q = o;     o = up256(o + static_cast<size_t>(M) * inter);
+  l.h_scale = o; o = up256(o + static_cast<size_t>(M) * 4);
+  l.total = o;
+  return l;
+}
+int mlp_run(sk_w2a8_plan* gu, sk_w2a8_plan* down, int64_t M, const void* x, int64_t ld_x, void* out, int64_t ld_out,
+            char* ws, sk_stream_t stream) {
+  const int64_t hidden = gu->K, inter = down->K;
+  const MlpLayout l = mlp_layout(M, hidden, inter);
+  int8_t* x_q = reinterpret_cast<int8_t*>(ws + l.x_q);
+  float* x_scale = reinterpret_cast<float*>(ws + l.x_scale);
+  void* gate_up = ws + l.gate_up;
+  int8_t* h_q = reinterpret_cast<int8_t*>(ws + l.h_q);
+  float* h_scale = reinterpret_cast<float*>(ws + l.h_scale);
+  int rc = sk_quantize_activation_int8(x, ld_x, M, hidden, x_q, hidden, x_scale, stream);
+  if (rc == SK_OK) rc = sk_w2a8_gemm(gu, M, x_q, hidden, x_scale, gate_up, 2 * inter, stream);
+  if (rc == SK_OK) rc = sk_silu_mul_quantize_int8(gate_up, 2 * inter, M, inter, h_q, inter, h_scale, stream);
+  if (rc == SK_OK) rc = sk_w2a8_gemm(down, M, h_q, inter, h_scale, out, ld_out, stream);
+  return rc;
+}
+int mlp_check(const sk_w2a8_plan* gu, const sk_w2a8_plan* down, int64_t M) {
+  if (!gu || !down) return SK_ERR_NULL_POINTER;
+  if (M <= 0) return SK_ERR_BAD_SHAPE;
+  if (gu->N != 2 * down->K || down->N != gu->K || gu->device != down->device) return SK_ERR_BAD_SHAPE;
+  if (gu->out_dtype != SK_OUT_F16) return SK_ERR_BAD_ARGUMENT;   // the SiLU kernel reads fp16
+  if ((gu->K % 16) != 0 || (down->K % 16) != 0) return SK_ERR_BAD_SHAPE;
+  return SK_OK;
+}
+}  // namespace
+
+int64_t sk_w2a8_mlp_workspace_bytes(const sk_w2a8_plan* gate_up, const sk_w2a8_plan* down, int64_t M) {
+  if (mlp_check(gate_up, down, M) != SK_OK) return 0;
+  return static_cast<int64_t>(mlp_layout(M, gate_up->K, down->K).total);
+}
+
+int sk_w2a8_mlp_forward(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, const void* x_f16, int64_t ld_x,
+                        void* out, int64_t ld_out, void* workspace, int64_t workspace_bytes, sk_stream_t stream) {
+  int rc = mlp_check(gate_up, down, M);
+  if (rc != SK_OK) return rc;
+  if (!x_f16 || !out || !workspace) return SK_ERR_NULL_POINTER;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return SK_ERR_BAD_ALIGNMENT;
+  if (workspace_bytes < static_cast<int64_t>(mlp_layout(M, gate_up->K, down->K).total)) return SK_ERR_BAD_SHAPE;
+  return mlp_run(gate_up, down, M, x_f16, ld_x, out, ld_out, static_cast<char*>(workspace), stream);
 }
 
 #ifdef SK_TRACE

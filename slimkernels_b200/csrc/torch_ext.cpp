@@ -105,6 +105,50 @@ at::Tensor partials(int64_t handle, const at::Tensor& x_q, int64_t N, int64_t K,
   return out;
 }
 
+std::tuple<at::Tensor, at::Tensor> quantize_activation(const at::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kHalf && x.dim() == 2 && x.stride(1) == 1,
+              "x must be a 2-D CUDA float16 tensor with unit inner stride");
+  const int64_t M = x.size(0), K = x.size(1);
+  at::Tensor q = at::empty({M, K}, x.options().dtype(at::kChar));
+  at::Tensor s = at::empty({M}, x.options().dtype(at::kFloat));
+  if (M == 0) return {q, s};
+  c10::cuda::CUDAGuard guard(x.device());
+  check(sk_quantize_activation_int8(x.data_ptr(), x.stride(0), M, K, q.data_ptr<int8_t>(), K, s.data_ptr<float>(),
+                                    at::cuda::getCurrentCUDAStream().stream()),
+        "quantize_activation_int8");
+  return {q, s};
+}
+
+std::tuple<at::Tensor, at::Tensor> silu_mul_quantize(const at::Tensor& gate_up) {
+  TORCH_CHECK(gate_up.is_cuda() && gate_up.scalar_type() == at::kHalf && gate_up.dim() == 2 && gate_up.stride(1) == 1 &&
+                  gate_up.size(1) % 2 == 0, "gate_up must be a 2-D CUDA float16 tensor [M, 2I]");
+  const int64_t M = gate_up.size(0), I = gate_up.size(1) / 2;
+  at::Tensor q = at::empty({M, I}, gate_up.options().dtype(at::kChar));
+  at::Tensor s = at::empty({M}, gate_up.options().dtype(at::kFloat));
+  if (M == 0) return {q, s};
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  check(sk_silu_mul_quantize_int8(gate_up.data_ptr(), gate_up.stride(0), M, I, q.data_ptr<int8_t>(), I,
+                                  s.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
+        "silu_mul_quantize_int8");
+  return {q, s};
+}
+
+at::Tensor mlp_forward(int64_t gate_up_plan, int64_t down_plan, const at::Tensor& x, int64_t hidden_out, bool bf16_out) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kHalf && x.dim() == 2 && x.stride(1) == 1,
+              "x must be a 2-D CUDA float16 tensor with unit inner stride");
+  const int64_t M = x.size(0);
+  at::Tensor out = at::empty({M, hidden_out}, x.options().dtype(bf16_out ? at::kBFloat16 : at::kHalf));
+  if (M == 0) return out;
+  const int64_t bytes = sk_w2a8_mlp_workspace_bytes(as_plan(gate_up_plan), as_plan(down_plan), M);
+  TORCH_CHECK(bytes > 0, "slimkernels::w2a8_mlp_forward: the two plans do not form an MLP block");
+  at::Tensor ws = at::empty({bytes}, x.options().dtype(at::kByte));     // caching allocator: 512-byte aligned
+  c10::cuda::CUDAGuard guard(x.device());
+  check(sk_w2a8_mlp_forward(as_plan(gate_up_plan), as_plan(down_plan), M, x.data_ptr(), x.stride(0), out.data_ptr(),
+                            out.stride(0), ws.data_ptr(), bytes, at::cuda::getCurrentCUDAStream().stream()),
+        "w2a8_mlp_forward");
+  return out;
+}
+
 int64_t device_status(int64_t handle) {
   int v = 0;
   int rc = sk_w2a8_last_device_status(as_plan(handle), &v);
@@ -144,6 +188,9 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_gemm_scatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int ld_out, int col_offset, int K) -> ()", &gemm_scatter);
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
+  m.def("quantize_activation_int8(Tensor x) -> (Tensor, Tensor)", &quantize_activation);
+  m.def("silu_mul_quantize_int8(Tensor gate_up) -> (Tensor, Tensor)", &silu_mul_quantize);
+  m.def("w2a8_mlp_forward(int gate_up_plan, int down_plan, Tensor x, int hidden_out, bool bf16_out) -> Tensor", &mlp_forward);
   m.def("w2a8_repack(Tensor w_packed) -> Tensor", &repack);
   m.def("w2a8_unrepack(Tensor w_tiled, int N, int K) -> Tensor", &unrepack);
 }
