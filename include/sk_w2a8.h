@@ -43,7 +43,8 @@ typedef enum sk_status {
   SK_ERR_DEVICE_TIMEOUT = -6,   /* a bounded wait inside a kernel expired; see sk_w2a8_last_device_status */
   SK_ERR_BAD_ARGUMENT = -7,
   SK_ERR_OUT_OF_MEMORY = -8,
-  SK_ERR_UNAVAILABLE = -9       /* requested kernel/option not available for this plan */
+  SK_ERR_UNAVAILABLE = -9,      /* requested kernel/option not available for this plan */
+  SK_ERR_STATIC_SCRATCH_TOO_SMALL = -10 /* sk_w2a8_mlp_forward_static: the problem exceeds the fixed buffer */
 } sk_status;
 
 typedef enum sk_out_dtype { SK_OUT_F16 = 0, SK_OUT_BF16 = 1 } sk_out_dtype;
@@ -118,6 +119,26 @@ int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M,
 int64_t sk_w2a8_mlp_workspace_bytes(const sk_w2a8_plan* gate_up, const sk_w2a8_plan* down, int64_t M);
 int sk_w2a8_mlp_forward(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, const void* x_f16, int64_t ld_x,
                         void* out, int64_t ld_out, void* workspace, int64_t workspace_bytes, sk_stream_t stream);
+
+/* The MLP block for hosts that must not allocate device memory while serving.  It has no counterpart in the
+ * reference.  Some embedders hand the GPU's memory to another owner at start-up (an inference server's arena, a
+ * game or robotics runtime with a fixed budget) or run where cudaMalloc is forbidden because it synchronises the
+ * device and can fail late; they can neither allocate the workspace sk_w2a8_mlp_forward asks for nor let a
+ * framework do it.  This entry point performs the same four launches with the intermediates in an 8 MiB array
+ * that is part of the library image (every GPU that loads the library holds those 8 MiB until the process
+ * exits).  It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are still the
+ * caller's.  Limits and rules:
+ *   - the intermediates must fit: M*hidden + 5*M*inter + 8*M bytes (each part rounded up to 256) <=
+ *     sk_w2a8_mlp_static_scratch_bytes(); e.g. Llama-2-7B (hidden 4096, inter 11008) up to M = 141 tokens.
+ *     Larger problems are refused with SK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device made
+ *     current); make that first call outside any stream capture;
+ *   - all calls on one GPU share the one array, which keeps whatever the previous call left in it (every byte a
+ *     call reads it has written first, so nothing needs clearing); two calls that overlap on the GPU — different
+ *     streams, or different threads — race on it.  Keep such calls on one stream or order them yourself. */
+int64_t sk_w2a8_mlp_static_scratch_bytes(void);
+int sk_w2a8_mlp_forward_static(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, const void* x_f16,
+                               int64_t ld_x, void* out, int64_t ld_out, sk_stream_t stream);
 
 /* -------- diagnostics -----------------------------------------------------------------------------*/
 /* Synchronously reads (and clears) the plan's device status word: 0, or a code naming the wait that

@@ -20,6 +20,7 @@ SK_ERR_DEVICE_TIMEOUT = -6
 SK_ERR_BAD_ARGUMENT = -7
 SK_ERR_OUT_OF_MEMORY = -8
 SK_ERR_UNAVAILABLE = -9
+SK_ERR_STATIC_SCRATCH_TOO_SMALL = -10
 
 SK_OUT_F16, SK_OUT_BF16 = 0, 1
 SK_WEIGHT_ROWMAJOR, SK_WEIGHT_TILED = 0, 1
@@ -43,6 +44,8 @@ SIGNATURES = {
     "sk_silu_mul_quantize_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "sk_w2a8_mlp_workspace_bytes": (_i64, [_vp, _vp, _i64]),
     "sk_w2a8_mlp_forward": (_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "sk_w2a8_mlp_static_scratch_bytes": (_i64, []),
+    "sk_w2a8_mlp_forward_static": (_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "sk_w2a8_last_device_status": (_int, [_vp, ctypes.POINTER(_int)]),
     "sk_w2a8_last_cuda_error": (_int, [_vp]),
     "sk_w2a8_query_launch": (_int, [_vp, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(_int),

@@ -421,6 +421,8 @@ const char* sk_status_string(int status) {
     case SK_ERR_BAD_ARGUMENT: return "bad argument";
     case SK_ERR_OUT_OF_MEMORY: return "out of device memory";
     case SK_ERR_UNAVAILABLE: return "not available for this plan";
+    case SK_ERR_STATIC_SCRATCH_TOO_SMALL:
+      return "problem needs more scratch than the library's fixed no-allocation buffer holds";
     default: return "unknown status";
   }
 }
@@ -471,6 +473,7 @@ int sk_w2a8_plan_create(sk_w2a8_plan** out, int device, int64_t N, int64_t K, in
   plan->n_tiles = static_cast<int>((N + 127) / 128);
   plan->sm_count = sms;
   plan->w_scale = static_cast<const __half*>(w_scale_f16);
+  plan->maps.reserve(17);   // the tensor-map cache never grows past 16 entries: no host reallocation on the call path
 
   int cur = -1;
   cudaGetDevice(&cur);
@@ -699,6 +702,50 @@ int sk_w2a8_mlp_forward(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, co
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return SK_ERR_BAD_ALIGNMENT;
   if (workspace_bytes < static_cast<int64_t>(mlp_layout(M, gate_up->K, down->K).total)) return SK_ERR_BAD_SHAPE;
   return mlp_run(gate_up, down, M, x_f16, ld_x, out, ld_out, static_cast<char*>(workspace), stream);
+}
+
+// ------------------------------------------------------------------------------------------------
+// MLP block without any allocation: the intermediates live in a fixed array that is part of the library image.
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kMlpStaticBytes = 8u << 20;   // 8 MiB per GPU that loads the library, held until the process exits
+static __device__ __align__(256) unsigned char g_mlp_static_scratch[kMlpStaticBytes];
+std::mutex g_static_mu;
+void* g_static_addr[64] = {nullptr};           // device address of the array, per device ordinal
+}  // namespace
+
+int64_t sk_w2a8_mlp_static_scratch_bytes(void) { return static_cast<int64_t>(kMlpStaticBytes); }
+
+int sk_w2a8_mlp_forward_static(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, const void* x_f16, int64_t ld_x,
+                               void* out, int64_t ld_out, sk_stream_t stream) {
+  int rc = mlp_check(gate_up, down, M);
+  if (rc != SK_OK) return rc;
+  if (!x_f16 || !out) return SK_ERR_NULL_POINTER;
+  if (mlp_layout(M, gate_up->K, down->K).total > kMlpStaticBytes) return SK_ERR_STATIC_SCRATCH_TOO_SMALL;
+  const int dev = gate_up->device;
+  if (dev < 0 || dev >= 64) return SK_ERR_BAD_ARGUMENT;
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) return sk::cuda_fail(gate_up, cudaGetLastError());
+  if (cur != dev && cudaSetDevice(dev) != cudaSuccess) return sk::cuda_fail(gate_up, cudaGetLastError());
+  void* scratch = nullptr;
+  {
+    // In host code the array's name is only a handle; the address a kernel can use has to be asked for, once
+    // per device and with that device current.
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_addr[dev]) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_mlp_static_scratch);
+      if (e != cudaSuccess || !p) {
+        if (cur != dev) (void)cudaSetDevice(cur);
+        return sk::cuda_fail(gate_up, e);
+      }
+      g_static_addr[dev] = p;
+    }
+    scratch = g_static_addr[dev];
+  }
+  rc = mlp_run(gate_up, down, M, x_f16, ld_x, out, ld_out, static_cast<char*>(scratch), stream);
+  if (cur != dev) (void)cudaSetDevice(cur);
+  return rc;
 }
 
 #ifdef SK_TRACE
