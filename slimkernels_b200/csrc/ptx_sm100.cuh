@@ -42,31 +42,20 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// One polling step.  The hint lets the hardware park the thread until the phase completes (or the hint
-// expires) instead of returning at once, so that a CTA full of waiting warps does not flood the shared-memory
-// pipe that the tensor-core and TMA instructions are issued through.
-#ifndef SK_SUSPEND_HINT_NS
-#define SK_SUSPEND_HINT_NS 20000
-#endif
+// One NON-BLOCKING polling step (mbarrier.test_wait).  Measured on B200: a poll costs ~14 cycles whether the
+// phase has completed or not, whereas mbarrier.try_wait parks the thread when the phase is still pending and a
+// parked thread resumes hundreds of cycles after the completion (and only after ~2600 cycles if nothing
+// completes).  Every hand-off of this kernel's pipeline is on the critical path of a K block, so all waits spin
+// on test_wait; the spins are short and bounded by the callers.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#if SK_SUSPEND_HINT_NS > 0
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(SK_SUSPEND_HINT_NS))
-      : "memory");
-#else
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
 
@@ -118,6 +107,17 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same, with the A operand read from tensor memory (lane = row, one 32-bit column = 4 consecutive K bytes,
+// so a K = 32 step is 8 columns).
+__device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]^T, fp16 operands, fp32 accumulators, K = 16 per instruction.
@@ -174,6 +174,18 @@ __device__ __forceinline__ void tmem_st_fill_32x16(uint32_t taddr, uint32_t v) {
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
       "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
       ::"r"(taddr), "r"(v)
+      : "memory");
+}
+// Store 32 registers into 32 consecutive columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -237,6 +249,12 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
   return v;
 }
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {   // volatile: may be re-issued after a wait
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");

@@ -208,11 +208,11 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   return c;
 }
 
-template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP>
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false>
 static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
                        cudaStream_t stream) {
-  using L = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>;
-  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, DUMP>;
+  using L = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>;
+  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, DUMP, A_TMEM>;
   static int configured_device_mask[64] = {0};
   if (plan->device < 64 && !configured_device_mask[plan->device]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -240,7 +240,7 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmPar
 
 constexpr int kAccBufsSmall = 4;   // accumulator buffers of the token tiles <= 128
 constexpr int kAccBufs256 = 2;     // 2 x 256 columns fill the tensor memory
-static int acc_bufs_of(int token_tile) { return token_tile == 256 ? kAccBufs256 : kAccBufsSmall; }
+static int acc_bufs_of(int token_tile) { return token_tile >= 192 ? kAccBufs256 : kAccBufsSmall; }
 
 // The running sum of one accumulator buffer must stay inside (-2^22, 2^22):
 // (K handled per buffer) * 127 * max|code - zp| < 2^22.
@@ -265,11 +265,14 @@ static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& 
                          int m_tiles, int split_k, cudaStream_t stream) {
   switch (token_tile) {
     // <tokens, epilogue warpgroups, expander warps, load stages, expanded stages, accumulator buffers>
-    case 16: return launch_umma<16, 1, 8, 8, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 32: return launch_umma<32, 1, 4, 6, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 64: return launch_umma<64, 1, 4, 6, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 128: return launch_umma<128, 2, 4, 4, 3, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 256: return launch_umma<256, 2, 4, 4, 3, kAccBufs256, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 16: return launch_umma<16, 1, 8, 4, 4, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 32: return launch_umma<32, 1, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 64: return launch_umma<64, 1, 4, 6, 6, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 128: return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    // 192 tokens: the expanded weights live in tensor memory (2 x 192 accumulator columns + 4 x 32 weight columns;
+    // no expanded-weight ring in shared memory, so the load ring is 7 stages deep)
+    case 192: return launch_umma<192, 2, 4, 7, 4, kAccBufs256, DUMP, true>(plan, map, prm, m_tiles, split_k, stream);
+    case 256: return launch_umma<256, 2, 4, 4, 4, kAccBufs256, DUMP>(plan, map, prm, m_tiles, split_k, stream);
     default: return SK_ERR_BAD_ARGUMENT;
   }
 }
@@ -318,7 +321,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
   LaunchChoice ch = choose(plan, M);
   if (partials) ch.split_k = 1;
   if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k)) {
-    if (ch.token_tile == 256 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1)) ch.token_tile = 128;
+    if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1)) ch.token_tile = 128;
     else return SK_ERR_BAD_SHAPE;   // K too deep for the int32 running sums of this tile configuration
   }
   int rc = SK_OK;
@@ -537,7 +540,7 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
       plan->opt_kernel = static_cast<int>(value);
       return SK_OK;
     case SK_OPT_TOKEN_TILE:
-      if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128 && value != 256)
+      if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128 && value != 192 && value != 256)
         return SK_ERR_BAD_ARGUMENT;
       plan->opt_token_tile = static_cast<int>(value);
       return SK_OK;

@@ -90,7 +90,7 @@ struct GemmParams {
 #endif
 };
 
-template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS>
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool A_TMEM = false>
 struct KernelTraits {
   static constexpr int kEpiWarps = EPI_WGS * 4;
   static constexpr int kWarps = ((kEpiWarps + EXP_WARPS + 2 + 3) / 4) * 4;   // whole warpgroups
@@ -101,11 +101,17 @@ struct KernelTraits {
   static constexpr int kColsPerWg = BLOCK_M / EPI_WGS;           // accumulators per epilogue thread
   static constexpr int kChunk = kColsPerWg >= 32 ? 32 : 16;      // TMEM columns per tcgen05.ld
   static constexpr int kNumChunks = kColsPerWg / kChunk;
-  static constexpr uint32_t kTmemCols = (ACC_BUFS * BLOCK_M < 32) ? 32 : ACC_BUFS * BLOCK_M;
+  // A_TMEM: the expanded weights go to tensor memory (32 columns per stage) instead of shared memory, which takes
+  // 32 KB of shared-memory traffic per K block off the pipe the tensor core reads its other operand through.
+  static constexpr int kAccCols = ACC_BUFS * BLOCK_M;
+  static constexpr int kATmemCol0 = kAccCols;                       // first column of the A stages
+  static constexpr int kTmemNeed = kAccCols + (A_TMEM ? ESTAGES * 32 : 0);
+  static constexpr uint32_t kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
+                                        : kTmemNeed <= 256 ? 256 : 512;
   static constexpr int kXBytes = BLOCK_M * kBlockK;
   static constexpr int kOffX = 0;
   static constexpr int kOffWx = kOffX + LSTAGES * kXBytes;
-  static constexpr int kOffWp = kOffWx + ESTAGES * kWxBytes;
+  static constexpr int kOffWp = kOffWx + (A_TMEM ? 0 : ESTAGES * kWxBytes);
   static constexpr int kOffBar = kOffWp + LSTAGES * kWpBytes;
   static constexpr int kNumBars = 2 * LSTAGES + 2 * ESTAGES + 2 * ACC_BUFS;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
@@ -117,7 +123,16 @@ struct KernelTraits {
   static_assert(BLOCK_M * kTileN * 4 <= kOffBar, "output staging must fit in the operand ring");
   static_assert(kColsPerWg % kChunk == 0 && kNumChunks >= 1, "bad epilogue split");
   static_assert(EXP_WARPS == 2 || EXP_WARPS == 4 || EXP_WARPS == 8, "expander warps");
-  static_assert((ACC_BUFS & (ACC_BUFS - 1)) == 0 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM");
+  static_assert((ACC_BUFS & (ACC_BUFS - 1)) == 0 && kTmemNeed <= 512, "TMEM");
+  static_assert(!A_TMEM || EXP_WARPS == 4, "TMEM-resident weights: one expander warp per lane quadrant");
+  // The expanded-weight ring is indexed like the load ring (stage i of one is stage i of the other): when the TMA
+  // data of stage i has landed, the MMAs that read the previous contents of stage i -- operands AND expanded
+  // weights -- have completed, because the producer refills a stage only after their commit.  That saves the
+  // expanders one barrier wait and one arrival per K block.
+  // With fewer expanded stages than load stages (a deep load ring hides the TMA latency; expanded stages cost
+  // 16 KB of shared memory or 32 TMEM columns each) a separate "expanded stage free" barrier is needed.
+  static constexpr bool kTied = (ESTAGES == LSTAGES);
+  static_assert(ESTAGES <= LSTAGES, "expanded stages");
   // Register budgets.  With two epilogue warpgroups the epilogue threads hold kColsPerWg accumulators plus two
   // sets of TMEM-load registers and take registers from the other warpgroup(s) with setmaxnreg.  The CTA's pool
   // is what it was given at launch (kLaunchRegs per thread); setmaxnreg.inc BLOCKS until the pool can serve it,
@@ -127,7 +142,7 @@ struct KernelTraits {
   //   BLOCK_M 128:                   512 threads, 128 at launch -> epilogue 168, others 88
   static constexpr bool kUseSetMaxNReg = (EPI_WGS == 2);
   static constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
-  static constexpr bool kBig = kColsPerWg > 64;
+  static constexpr bool kBig = kColsPerWg > 96;
   static constexpr int kEpiRegs = kBig ? (kThreads == 384 ? 224 : 216) : 168;
   static constexpr int kExpRegs = kBig ? 48 : 88;                         // warpgroup holding the expander warps
   static constexpr int kCtlRegs = kBig ? (kThreads == 384 ? 56 : 32) : 88;   // warpgroup holding producer + MMA warps
@@ -193,11 +208,11 @@ __device__ __forceinline__ void tmem_fill_chunk(uint32_t taddr, uint32_t value) 
   if constexpr (CHUNK == 32) tmem_st_fill_32x32(taddr, value); else tmem_st_fill_32x16(taddr, value);
 }
 
-template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP>
-__global__ void __launch_bounds__(KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>::kThreads,
-                                  KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>::kMinBlocks)
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false>
+__global__ void __launch_bounds__(KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>::kThreads,
+                                  KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>::kMinBlocks)
 w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-  using T = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS>;
+  using T = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>;
   constexpr int kChunk = T::kChunk;
   constexpr int kNumChunks = T::kNumChunks;
   constexpr int kCols = T::kColsPerWg;
@@ -214,7 +229,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
   const uint32_t bar_ld_full = bar_base;
   const uint32_t bar_ld_empty = bar_ld_full + 8u * LSTAGES;
   const uint32_t bar_ex_full = bar_ld_empty + 8u * LSTAGES;
-  const uint32_t bar_ex_empty = bar_ex_full + 8u * ESTAGES;
+  const uint32_t bar_ex_empty = bar_ex_full + 8u * ESTAGES;      // used only when the rings are not tied
   const uint32_t bar_acc_full = bar_ex_empty + 8u * ESTAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 8u * ACC_BUFS;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::kOffMisc);
@@ -247,8 +262,14 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
   // Every mbarrier counts ONE arrival per participating warp (lane 0, after __syncwarp): arrivals on one
   // barrier are serialised shared-memory atomics.
   if (threadIdx.x == 0) {
-    for (int i = 0; i < LSTAGES; ++i) { mbar_init(bar_ld_full + 8 * i, 1); mbar_init(bar_ld_empty + 8 * i, 1 + EXP_WARPS); }
-    for (int i = 0; i < ESTAGES; ++i) { mbar_init(bar_ex_full + 8 * i, EXP_WARPS); mbar_init(bar_ex_empty + 8 * i, 1); }
+    for (int i = 0; i < LSTAGES; ++i) {
+      mbar_init(bar_ld_full + 8 * i, 1);           // TMA transaction bytes
+      mbar_init(bar_ld_empty + 8 * i, 1);          // tcgen05.commit of the MMAs that read the stage
+    }
+    for (int i = 0; i < ESTAGES; ++i) {
+      mbar_init(bar_ex_full + 8 * i, EXP_WARPS);   // expanded weights of the stage are in place
+      mbar_init(bar_ex_empty + 8 * i, 1);          // commit of the MMAs that read them (untied rings only)
+    }
     for (int i = 0; i < ACC_BUFS; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -330,16 +351,30 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
             const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(l * (T::kXBytes >> 4));
             const uint32_t d = tmem_base + ab * BLOCK_M;
             // +2 in the (address >> 4) field advances 32 bytes along K inside the 128-byte swizzle row
-            umma_i8(d, a_desc, b_desc, idesc, 1u);
-            umma_i8(d, a_desc + 2, b_desc + 2, idesc, 1u);
-            umma_i8(d, a_desc + 4, b_desc + 4, idesc, 1u);
-            umma_i8(d, a_desc + 6, b_desc + 6, idesc, 1u);
+            if constexpr (A_TMEM) {
+              const uint32_t a_t = tmem_base + T::kATmemCol0 + e * 32;   // 8 columns per 32-wide K step
+              umma_i8_ts(d, a_t, b_desc, idesc, 1u);
+              umma_i8_ts(d, a_t + 8, b_desc + 2, idesc, 1u);
+              umma_i8_ts(d, a_t + 16, b_desc + 4, idesc, 1u);
+              umma_i8_ts(d, a_t + 24, b_desc + 6, idesc, 1u);
+            } else {
+              umma_i8(d, a_desc, b_desc, idesc, 1u);
+              umma_i8(d, a_desc + 2, b_desc + 2, idesc, 1u);
+              umma_i8(d, a_desc + 4, b_desc + 4, idesc, 1u);
+              umma_i8(d, a_desc + 6, b_desc + 6, idesc, 1u);
+            }
             umma_commit(bar_acc_full + 8 * ab);
             umma_commit(bar_ld_empty + 8 * l);
-            umma_commit(bar_ex_empty + 8 * e);
+            if constexpr (!T::kTied) umma_commit(bar_ex_empty + 8 * e);
             SK_TRACE_EVENT(2, kb - kb_begin);
           }
           __syncwarp();
+#ifdef SK_TRACE_MMA_LATENCY
+          if (kb - kb_begin >= 8 && kb - kb_begin < 24) {   // diagnostic: how long do the 4 MMAs take to complete?
+            while (!mbar_try_wait(bar_acc_full + 8 * ab, aph)) {}
+            if (lane == 0) SK_TRACE_EVENT(5, kb - kb_begin);
+          }
+#endif
           if (++l == LSTAGES) { l = 0; lph ^= 1; }
           if (++e == ESTAGES) { e = 0; eph ^= 1; }
           if (++ab == ACC_BUFS) { ab = 0; aph ^= 1; }
@@ -365,7 +400,10 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
             }
             const bool last = (pos == p.steps_per_group - 1);
             if (elect_one()) {
-              umma_i8(tmem_base + ab * BLOCK_M, a_desc + 2 * s, b_desc + 2 * s, idesc, 1u);
+              if constexpr (A_TMEM)
+                umma_i8_ts(tmem_base + ab * BLOCK_M, tmem_base + T::kATmemCol0 + e * 32 + 8 * s, b_desc + 2 * s, idesc, 1u);
+              else
+                umma_i8(tmem_base + ab * BLOCK_M, a_desc + 2 * s, b_desc + 2 * s, idesc, 1u);
               if (last) umma_commit(bar_acc_full + 8 * ab);
             }
             __syncwarp();
@@ -379,7 +417,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
           if (!ok) break;
           if (elect_one()) {
             umma_commit(bar_ld_empty + 8 * l);
-            umma_commit(bar_ex_empty + 8 * e);
+            if constexpr (!T::kTied) umma_commit(bar_ex_empty + 8 * e);
           }
           __syncwarp();
           if (++l == LSTAGES) { l = 0; lph ^= 1; }
@@ -408,36 +446,53 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         wp_off[rr] = T::kOffWp + row * 16 + half * 2048;
       }
       for (int kb = kb_begin; kb < kb_end; ++kb) {
-        // poll both barriers at once; the slow paths only run when a poll failed
-        const bool r1 = mbar_try_wait(bar_ld_full + 8 * l, lph);
-        const bool r2 = mbar_try_wait(bar_ex_empty + 8 * e, eph ^ 1);
-        if (!r1 && !wait_slow(bar_ld_full + 8 * l, lph, ctx.abort_flag, ctx.status, kStExpanderFull)) break;
-        if (!r2 && !wait_slow(bar_ex_empty + 8 * e, eph ^ 1, ctx.abort_flag, ctx.status, kStExpanderEmpty)) break;
+        // The loads below must not be issued before the wait has been seen to succeed: a load that does not depend
+        // on the poll's predicate can be served before the barrier state is sampled and return stale bytes.
+        if (!wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStExpanderFull)) break;
+        if constexpr (!T::kTied) {
+          if (!wait_bounded(bar_ex_empty + 8 * e, eph ^ 1, ctx, kStExpanderEmpty)) break;
+        }
+        const uint32_t wp = smem_base + wp_off[0] + l * kWpBytes;
+        const uint4 q0 = ld_shared_v4(wp);
+        const uint4 q1 = kHalfRows ? make_uint4(0, 0, 0, 0) : ld_shared_v4(wp + 2048);
+        if constexpr (A_TMEM) {
+          // this thread's row (= its TMEM lane): 32 bytes of codes in, 128 int8 bytes out as 32 TMEM columns
+          const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          uint32_t a_row[32];
 #pragma unroll
-        for (int rr = 0; rr < T::kRowsPerExpThread; ++rr) {
-          const uint8_t* wp = smem + wp_off[rr] + l * kWpBytes;
-          const uint32_t wx = smem_base + wx_off[rr] + e * kWxBytes;
+          for (int c = 0; c < 8; ++c) {
+            const uint4 o = expand16(words[c], lut);
+            a_row[4 * c] = o.x; a_row[4 * c + 1] = o.y; a_row[4 * c + 2] = o.z; a_row[4 * c + 3] = o.w;
+          }
+          tmem_st_32x32(tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + T::kATmemCol0 + e * 32, a_row);
+          tmem_st_wait();
+          tcgen05_fence_before_sync();
+        } else {
+          const uint32_t wx = smem_base + wx_off[0] + e * kWxBytes;
           if constexpr (kHalfRows) {
             // 16 bytes in (codes 64 half .. +63 of this row), 64 bytes out
-            const uint4 q = *reinterpret_cast<const uint4*>(wp);
-            const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+            const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
 #pragma unroll
             for (int c = 0; c < 4; ++c) st_shared_v4(wx ^ ((4 * half + c) << 4), expand16(words[c], lut));
           } else {
             // 2 x 16 bytes in (codes 0..63 and 64..127 of this row), 128 bytes out
-            const uint4 q0 = *reinterpret_cast<const uint4*>(wp);
-            const uint4 q1 = *reinterpret_cast<const uint4*>(wp + 2048);
             const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
             for (int c = 0; c < 8; ++c) st_shared_v4(wx ^ (c << 4), expand16(words[c], lut));
           }
+          if constexpr (T::kRowsPerExpThread == 2) {    // two rows per thread: the second row, read after the wait
+            const uint8_t* wp2 = smem + wp_off[1] + l * kWpBytes;
+            const uint32_t wx2 = smem_base + wx_off[1] + e * kWxBytes;
+            const uint4 r0 = *reinterpret_cast<const uint4*>(wp2);
+            const uint4 r1 = *reinterpret_cast<const uint4*>(wp2 + 2048);
+            const uint32_t words2[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) st_shared_v4(wx2 ^ (c << 4), expand16(words2[c], lut));
+          }
+          fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
         }
-        fence_proxy_async_smem();   // make the generic-proxy stores visible to the tensor core's async proxy
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar_ld_empty + 8 * l);
-          mbar_arrive(bar_ex_full + 8 * e);
-        }
+        if (lane == 0) mbar_arrive(bar_ex_full + 8 * e);
         if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, kb - kb_begin);
         if (++l == LSTAGES) { l = 0; lph ^= 1; }
         if (++e == ESTAGES) { e = 0; eph ^= 1; }

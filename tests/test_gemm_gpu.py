@@ -68,12 +68,12 @@ def test_config0_full(zp):
     _check(prob, 128, zp)
 
 
-@pytest.mark.parametrize("token_tile", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("token_tile", [16, 32, 64, 128, 192, 256])
 @pytest.mark.parametrize("split_k", [1, 2, 4, 8])
 def test_every_tile_and_split(token_tile, split_k):
     if token_tile >= 128 and split_k > 1:
         pytest.skip("split-K is for small token tiles")
-    M = {16: 13, 32: 32, 64: 70, 128: 200, 256: 300}[token_tile]
+    M = {16: 13, 32: 32, 64: 70, 128: 200, 192: 400, 256: 300}[token_tile]
     prob = random_problem(M, 384, 1024, 128, seed=token_tile + split_k)
     _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, split_k=split_k))
 
