@@ -59,7 +59,9 @@ typedef enum sk_weight_layout {
 typedef enum sk_option {
   SK_OPT_KERNEL = 1,      /* 0 auto, 1 tcgen05 kernel, 2 CUDA-core checker kernel (needs SK_WEIGHT_ROWMAJOR) */
   SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 / 192 / 256 */
-  SK_OPT_SPLIT_K = 3      /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
+  SK_OPT_SPLIT_K = 3,     /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
+  SK_OPT_PERSISTENT = 4   /* 0 auto (= 1), 1 one CTA per tile, 2 one resident set of CTAs walks all tiles (token tiles
+                             128 / 256 without split-K, when there are more tiles than the GPU holds at once) */
 } sk_option;
 
 /* -------- weight preparation ("Blackwell tile order") ------------------------------------------

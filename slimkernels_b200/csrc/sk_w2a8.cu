@@ -163,7 +163,7 @@ struct sk_w2a8_plan {
   const __half* w_scale = nullptr;      // borrowed
   int* status = nullptr;                // device, owned
   int last_cuda_error = 0;
-  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0;
+  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0;
   std::vector<sk::CachedMap> maps;      // small cache of activation tensor maps
   std::mutex mu;
 };
@@ -184,6 +184,8 @@ struct LaunchChoice {
   int kernel;      // 1 tcgen05, 2 CUDA-core checker
   int token_tile;  // 16 / 32 / 64 / 128
   int split_k;     // 1 / 2 / 4 / 8
+  int persistent;  // 1: one resident set of CTAs walks all tiles
+  int ctas;        // CTAs launched
 };
 
 static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
@@ -205,14 +207,24 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   }
   if (c.split_k > groups) c.split_k = 1;
   if (c.token_tile > 64) c.split_k = 1;   // the cluster reduction buffer is sized for small token tiles
+  // With more tiles than the machine holds at once, one resident set of CTAs can walk the tiles instead (option
+  // SK_OPT_PERSISTENT = 2): the pipeline of the next tile fills while the previous tile is written out through TMA
+  // stores.  Measured on B200 it is not reliably faster than one CTA per tile (all CTAs then move in lock-step and
+  // hit L2 in bursts), so it is not the default.
+  const long long tiles = plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile);
+  const long long capacity = static_cast<long long>(plan->sm_count) * (c.token_tile <= 32 ? 2 : 1);
+  c.persistent = (plan->opt_persistent == 2 && tiles > capacity) ? 1 : 0;
+  if (c.split_k > 1 || (c.token_tile != 128 && c.token_tile != 256)) c.persistent = 0;
+  c.ctas = static_cast<int>(c.persistent ? (tiles < capacity ? tiles : capacity) : tiles * c.split_k);
   return c;
 }
 
-template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false>
-static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
-                       cudaStream_t stream) {
-  using L = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>;
-  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, DUMP, A_TMEM>;
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false,
+          bool PERSIST = false>
+static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtensorMap& out_map, const GemmParams& prm,
+                       int m_tiles, int split_k, int persistent_ctas, cudaStream_t stream) {
+  using L = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>;
+  auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, DUMP, A_TMEM, PERSIST>;
   static int configured_device_mask[64] = {0};
   if (plan->device < 64 && !configured_device_mask[plan->device]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -220,7 +232,7 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmPar
     configured_device_mask[plan->device] = 1;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(plan->n_tiles, m_tiles, split_k);
+  cfg.gridDim = PERSIST ? dim3(static_cast<unsigned>(persistent_ctas), 1, 1) : dim3(plan->n_tiles, m_tiles, split_k);
   cfg.blockDim = dim3(L::kThreads, 1, 1);
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
@@ -233,7 +245,7 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmPar
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, prm);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, out_map, prm);
   if (e != cudaSuccess) return cuda_fail(plan, e);
   return SK_OK;
 }
@@ -261,18 +273,26 @@ __global__ void diff_partials_kernel(int32_t* __restrict__ partials, int groups,
 }
 
 template <bool DUMP>
-static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const GemmParams& prm,
-                         int m_tiles, int split_k, cudaStream_t stream) {
+static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const CUtensorMap& out_map,
+                         const GemmParams& prm, int m_tiles, int split_k, int persistent_ctas, cudaStream_t stream) {
   switch (token_tile) {
     // <tokens, epilogue warpgroups, expander warps, load stages, expanded stages, accumulator buffers>
-    case 16: return launch_umma<16, 1, 8, 4, 4, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 32: return launch_umma<32, 1, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 64: return launch_umma<64, 1, 4, 6, 6, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
-    case 128: return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 16: return launch_umma<16, 1, 8, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 32: return launch_umma<32, 1, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 64: return launch_umma<64, 1, 4, 6, 6, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 128:
+      if constexpr (!DUMP)
+        if (persistent_ctas > 0)
+          return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, false, false, true>(plan, map, out_map, prm, m_tiles, 1, persistent_ctas, stream);
+      return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
     // 192 tokens: the expanded weights live in tensor memory (2 x 192 accumulator columns + 4 x 32 weight columns;
     // no expanded-weight ring in shared memory, so the load ring is 7 stages deep)
-    case 192: return launch_umma<192, 2, 4, 7, 4, kAccBufs256, DUMP, true>(plan, map, prm, m_tiles, split_k, stream);
-    case 256: return launch_umma<256, 2, 4, 4, 4, kAccBufs256, DUMP>(plan, map, prm, m_tiles, split_k, stream);
+    case 192: return launch_umma<192, 2, 4, 7, 4, kAccBufs256, DUMP, true>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 256:
+      if constexpr (!DUMP)
+        if (persistent_ctas > 0)
+          return launch_umma<256, 2, 4, 4, 2, kAccBufs256, false, false, true>(plan, map, out_map, prm, m_tiles, 1, persistent_ctas, stream);
+      return launch_umma<256, 2, 4, 4, 4, kAccBufs256, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
     default: return SK_ERR_BAD_ARGUMENT;
   }
 }
@@ -297,6 +317,30 @@ static int get_x_map(sk_w2a8_plan* plan, const int8_t* x_q, long long M, long lo
   if (plan->maps.size() >= 16) plan->maps.erase(plan->maps.begin());
   plan->maps.push_back(cm);
   *out = cm.map;
+  return SK_OK;
+}
+
+// Tensor map of an output buffer for the TMA stores of the persistent kernel: 16-bit elements, [M][N] with row
+// pitch ld_out, boxes of 128 features x 64 tokens, no swizzle.
+static int get_out_map(sk_w2a8_plan* plan, const void* out, long long M, long long ld_out, CUtensorMap* res) {
+  std::lock_guard<std::mutex> lock(plan->mu);
+  for (const auto& c : plan->maps)
+    if (c.ptr == out && c.M == M && c.ld == ld_out && c.block_m == -1) { *res = c.map; return SK_OK; }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return SK_ERR_CUDA;
+  CachedMap cm;
+  cm.ptr = out; cm.M = M; cm.ld = ld_out; cm.block_m = -1;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(plan->N), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_out) * 2};
+  const cuuint32_t box[2] = {128u, 64u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(&cm.map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(out), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { plan->last_cuda_error = static_cast<int>(r); return SK_ERR_CUDA; }
+  if (plan->maps.size() >= 16) plan->maps.erase(plan->maps.begin());
+  plan->maps.push_back(cm);
+  *res = cm.map;
   return SK_OK;
 }
 
@@ -363,9 +407,26 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.trace = g_trace_buffer;
 #endif
       const int m_tiles = static_cast<int>((M + ch.token_tile - 1) / ch.token_tile);
+      prm.n_tiles = plan->n_tiles;
+      prm.num_tiles = plan->n_tiles * m_tiles;
+      // The persistent kernel stores through TMA (and 16-byte vectors for further destinations): the output must be
+      // 16-byte aligned with a pitch that is a multiple of 8 elements, N a multiple of 8 (the tensor map's extent in
+      // bytes), and with further destinations the feature tiles must be whole.
+      bool persist = ch.persistent && !partials && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
+                     (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+      if (persist && n_extra > 0) {
+        if (plan->N % 128) persist = false;
+        for (int i = 0; i < n_extra; ++i)
+          if (reinterpret_cast<uintptr_t>(extra_outs[i]) & 15) persist = false;
+      }
+      CUtensorMap out_map = map;   // placeholder where the kernel does not use it
+      if (persist) {
+        rc = get_out_map(plan, out, M, ld_out, &out_map);
+        if (rc != SK_OK) persist = false, rc = SK_OK;
+      }
       if (m_tiles > 65535) rc = SK_ERR_BAD_SHAPE;
       else if (partials) {
-        rc = dispatch_umma<true>(plan, ch.token_tile, map, prm, m_tiles, 1, stream);
+        rc = dispatch_umma<true>(plan, ch.token_tile, map, out_map, prm, m_tiles, 1, 0, stream);
         if (rc == SK_OK) {
           const long long mn = M * plan->N;
           const int blocks = static_cast<int>(mn / 256 + 1 < 148 * 8 ? mn / 256 + 1 : 148 * 8);
@@ -374,7 +435,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
           if (e != cudaSuccess) rc = cuda_fail(plan, e);
         }
       }
-      else rc = dispatch_umma<false>(plan, ch.token_tile, map, prm, m_tiles, ch.split_k, stream);
+      else rc = dispatch_umma<false>(plan, ch.token_tile, map, out_map, prm, m_tiles, ch.split_k, persist ? ch.ctas : 0, stream);
     }
   }
   if (cur != plan->device) (void)cudaSetDevice(cur);
@@ -512,6 +573,7 @@ int sk_w2a8_plan_create(sk_w2a8_plan** out, int device, int64_t N, int64_t K, in
   if (rc != SK_OK) {
     if (plan->status) cudaFree(plan->status);
     if (plan->w_tiled_owned) cudaFree(plan->w_tiled_owned);
+
     delete plan;
     return rc;
   }
@@ -547,6 +609,10 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
     case SK_OPT_SPLIT_K:
       if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SK_ERR_BAD_ARGUMENT;
       plan->opt_split_k = static_cast<int>(value);
+      return SK_OK;
+    case SK_OPT_PERSISTENT:
+      if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_persistent = static_cast<int>(value);
       return SK_OK;
     default: return SK_ERR_BAD_ARGUMENT;
   }
@@ -601,7 +667,7 @@ int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* sp
   const sk::LaunchChoice c = sk::choose(plan, M);
   if (token_tile) *token_tile = c.token_tile;
   if (split_k) *split_k = c.split_k;
-  if (ctas) *ctas = static_cast<int>(plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile) * c.split_k);
+  if (ctas) *ctas = c.ctas;
   if (kernel_kind) *kernel_kind = c.kernel;
   return SK_OK;
 }

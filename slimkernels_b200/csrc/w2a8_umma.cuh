@@ -47,6 +47,7 @@ constexpr int kBlockK = 128;         // K codes per pipeline stage (= one 128-by
 constexpr int kWpBytes = kTileN * kBlockK / 4;   // 4096: tiled 2-bit block
 constexpr int kWxBytes = kTileN * kBlockK;       // 16384: expanded int8 block
 constexpr long long kWaitLimitCycles = 1000000000ll;  // every mbarrier wait gives up after 1e9 SM cycles (0.5-0.8 s)
+constexpr int kScalePrefetchGroups = 8;   // group scales are pulled into L2 this many groups before they are loaded
 constexpr int kBiasFlushGroups = 16;  // the bias term is subtracted from the accumulators this often
 
 // device status codes: role * 16 + barrier kind
@@ -65,8 +66,10 @@ enum : int {
     if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 64)           \
       p.trace[(role) * 64 + (idx)] = clock64();                                                   \
   } while (0)
+#define SK_TRACE_BASE (((tile - tile_first) / tile_step) * (kb_end - kb_begin))   /* events of earlier tiles */
 #else
 #define SK_TRACE_EVENT(role, idx) do { } while (0)
+#define SK_TRACE_BASE 0
 #endif
 
 struct GemmParams {
@@ -85,12 +88,15 @@ struct GemmParams {
   int groups;                 // K / G
   int zero_point;
   int out_bf16;
+  int n_tiles;                // ceil(N / 128)
+  int num_tiles;              // n_tiles * token tiles
 #ifdef SK_TRACE
   long long* trace;           // [8][64] clock stamps of CTA (0,0,0)
 #endif
 };
 
-template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool A_TMEM = false>
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool A_TMEM = false,
+          bool PERSIST = false>
 struct KernelTraits {
   static constexpr int kEpiWarps = EPI_WGS * 4;
   static constexpr int kWarps = ((kEpiWarps + EXP_WARPS + 2 + 3) / 4) * 4;   // whole warpgroups
@@ -112,15 +118,21 @@ struct KernelTraits {
   static constexpr int kOffX = 0;
   static constexpr int kOffWx = kOffX + LSTAGES * kXBytes;
   static constexpr int kOffWp = kOffWx + (A_TMEM ? 0 : ESTAGES * kWxBytes);
-  static constexpr int kOffBar = kOffWp + LSTAGES * kWpBytes;
+  // Persistent CTAs write the output through a staging area of their own (the ring belongs to the next tile by
+  // then): kStageTokens tokens x 128 features x 16 bit per epilogue warpgroup, sent with TMA stores.
+  static constexpr int kStageTokens = 64;
+  static constexpr int kStageBytes = kStageTokens * kTileN * 2;                  // 16 KB per warpgroup
+  static constexpr int kOffStage = kOffWp + LSTAGES * kWpBytes;
+  static constexpr int kOffBar = kOffStage + (PERSIST ? EPI_WGS * kStageBytes : 0);
   static constexpr int kNumBars = 2 * LSTAGES + 2 * ESTAGES + 2 * ACC_BUFS;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
-  static constexpr int kOffXs = kOffMisc + 16;                   // fp32 [BLOCK_M]: x_scale of the tile's tokens
-  static constexpr int kTotal = kOffXs + BLOCK_M * 4;
+  static constexpr int kOffXs = kOffMisc + 16;                   // fp32 [2][BLOCK_M]: x_scale of the tile's tokens
+  static constexpr int kTotal = kOffXs + 2 * BLOCK_M * 4;
   static constexpr int kDynamicBytes = kTotal + 1024;            // slack for 1024-byte alignment of the base
   // After the main loop the operand ring is dead and is reused for the output tile
   // (fp32 [BLOCK_M][128] for the split-K reduction, 16-bit [BLOCK_M][128] otherwise).
-  static_assert(BLOCK_M * kTileN * 4 <= kOffBar, "output staging must fit in the operand ring");
+  static_assert(BLOCK_M * kTileN * 4 <= kOffStage, "output staging must fit in the operand ring");
+  static_assert(!PERSIST || (EPI_WGS == 2 && (BLOCK_M / EPI_WGS) % kStageTokens == 0), "persistent output rounds");
   static_assert(kColsPerWg % kChunk == 0 && kNumChunks >= 1, "bad epilogue split");
   static_assert(EXP_WARPS == 2 || EXP_WARPS == 4 || EXP_WARPS == 8, "expander warps");
   static_assert((ACC_BUFS & (ACC_BUFS - 1)) == 0 && kTmemNeed <= 512, "TMEM");
@@ -137,15 +149,15 @@ struct KernelTraits {
   // sets of TMEM-load registers and take registers from the other warpgroup(s) with setmaxnreg.  The CTA's pool
   // is what it was given at launch (kLaunchRegs per thread); setmaxnreg.inc BLOCKS until the pool can serve it,
   // so the budgets must add up to no more than the pool or the kernel hangs:
-  //   BLOCK_M 256, 4 expander warps: 512 threads, 128 at launch -> epilogue 216, expanders 48, control 32
+  //   BLOCK_M 256, 4 expander warps: 512 threads, 128 at launch -> epilogue 216, expanders 40, control 40
   //   BLOCK_M 256, 2 expander warps: 384 threads, 168 at launch -> epilogue 224, expanders + control 56
   //   BLOCK_M 128:                   512 threads, 128 at launch -> epilogue 168, others 88
   static constexpr bool kUseSetMaxNReg = (EPI_WGS == 2);
   static constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
   static constexpr bool kBig = kColsPerWg > 96;
   static constexpr int kEpiRegs = kBig ? (kThreads == 384 ? 224 : 216) : 168;
-  static constexpr int kExpRegs = kBig ? 48 : 88;                         // warpgroup holding the expander warps
-  static constexpr int kCtlRegs = kBig ? (kThreads == 384 ? 56 : 32) : 88;   // warpgroup holding producer + MMA warps
+  static constexpr int kExpRegs = kBig ? 40 : 88;                         // warpgroup holding the expander warps
+  static constexpr int kCtlRegs = kBig ? (kThreads == 384 ? 56 : 40) : 88;   // warpgroup holding producer + MMA warps
   static constexpr int kExpWgThreads = (EXP_WARPS == 4) ? 128 : 0;        // expanders have a warpgroup of their own
   static_assert(!kUseSetMaxNReg ||
                     kEpiThreads * kEpiRegs + kExpWgThreads * kExpRegs +
@@ -199,6 +211,38 @@ __device__ __forceinline__ uint4 expand16(uint32_t w, uint32_t lut) {
   return o;
 }
 
+// Output staging: COUNT tokens of one feature (this thread's accumulators acc[j0 .. j0+COUNT), times the token scales
+// xs[0 .. COUNT) in shared memory) -> 16-bit values at dst[t * kTileN], t = 0 .. COUNT-1.
+// Two tokens per conversion instruction (the f32 -> f16 conversion unit runs at a quarter of the FMA rate), the
+// scales fetched four at a time, eight tokens in flight so that the load/multiply/convert/store latencies overlap.
+template <int COUNT, bool BF16, int NACC>
+__device__ __forceinline__ void stage_tokens(const float (&acc)[NACC], int j0, const float* xs, uint16_t* dst) {
+  static_assert(COUNT % 8 == 0, "tokens per staging call");
+#pragma unroll
+  for (int b = 0; b < COUNT; b += 8) {
+    const float4 s0 = *reinterpret_cast<const float4*>(xs + b);
+    const float4 s1 = *reinterpret_cast<const float4*>(xs + b + 4);
+    const float y[8] = {acc[j0 + b] * s0.x,     acc[j0 + b + 1] * s0.y, acc[j0 + b + 2] * s0.z, acc[j0 + b + 3] * s0.w,
+                        acc[j0 + b + 4] * s1.x, acc[j0 + b + 5] * s1.y, acc[j0 + b + 6] * s1.z, acc[j0 + b + 7] * s1.w};
+    uint32_t h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+        h[i] = *reinterpret_cast<const uint32_t*>(&v);
+      } else {
+        const __half2 v = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+        h[i] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dst[(b + 2 * i) * kTileN] = static_cast<uint16_t>(h[i]);
+      dst[(b + 2 * i + 1) * kTileN] = static_cast<uint16_t>(h[i] >> 16);
+    }
+  }
+}
+
 template <int CHUNK>
 __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&v)[CHUNK]) {
   if constexpr (CHUNK == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
@@ -208,11 +252,13 @@ __device__ __forceinline__ void tmem_fill_chunk(uint32_t taddr, uint32_t value) 
   if constexpr (CHUNK == 32) tmem_st_fill_32x32(taddr, value); else tmem_st_fill_32x16(taddr, value);
 }
 
-template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false>
-__global__ void __launch_bounds__(KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>::kThreads,
-                                  KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>::kMinBlocks)
-w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-  using T = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM>;
+template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false,
+          bool PERSIST = false>
+__global__ void __launch_bounds__(KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>::kThreads,
+                                  KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>::kMinBlocks)
+w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_out,
+                 const GemmParams p) {
+  using T = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>;
   constexpr int kChunk = T::kChunk;
   constexpr int kNumChunks = T::kNumChunks;
   constexpr int kCols = T::kColsPerWg;
@@ -238,12 +284,14 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x;
-  const int m_tile = blockIdx.y;
   const int split = blockIdx.z;
   const int num_splits = gridDim.z;
-  const int n0 = n_tile * kTileN;
-  const int m0 = m_tile * BLOCK_M;
+  // Tiles are numbered feature-tile fastest.  A persistent CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...:
+  // its rings, barrier phases and accumulator buffers simply carry on from one tile to the next, so the loads,
+  // the expansion and the MMAs of the next tile start while the epilogue still writes the previous one.
+  const int tile_first = static_cast<int>(blockIdx.x + blockIdx.y * gridDim.x);   // persistent: gridDim.y == 1
+  const int tile_end = PERSIST ? p.num_tiles : tile_first + 1;
+  const int tile_step = PERSIST ? static_cast<int>(gridDim.x) : 1;
 
   // K range of this CTA, in whole scale groups.
   const int groups_per_split = (p.groups + num_splits - 1) / num_splits;
@@ -274,7 +322,10 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == kProducerWarp && lane == 0) prefetch_tensormap(&tmap_x);
+  if (warp == kProducerWarp && lane == 0) {
+    prefetch_tensormap(&tmap_x);
+    if constexpr (PERSIST) prefetch_tensormap(&tmap_out);
+  }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), T::kTmemCols);
     tmem_relinquish();
@@ -292,28 +343,32 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
     }
     if (warp == kProducerWarp) {
       // ============================================================ producer (whole warp loops, one lane issues)
-      const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
       uint32_t dst_wp = smem_base + T::kOffWp, dst_x = smem_base + T::kOffX;
       uint32_t full = bar_ld_full, empty = bar_ld_empty;
       int stage = 0, issued = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kcoord = kb_begin * kBlockK; kcoord < kb_end * kBlockK; kcoord += kBlockK) {
-        ok = wait_bounded(empty, phase ^ 1, ctx, kStProducerEmpty);
-        if (!ok) break;
-        if (elect_one()) {
-          SK_TRACE_EVENT(0, issued);
-          mbar_arrive_expect_tx(full, kStageTxBytes);
-          bulk_load_1d(dst_wp, wsrc, kWpBytes, full);
-          tma_load_2d(dst_x, &tmap_x, kcoord, m0, full);
-        }
-        __syncwarp();
-        wsrc += kWpBytes; ++issued;
-        if (++stage == LSTAGES) {
-          stage = 0; phase ^= 1;
-          dst_wp = smem_base + T::kOffWp; dst_x = smem_base + T::kOffX; full = bar_ld_full; empty = bar_ld_empty;
-        } else {
-          dst_wp += kWpBytes; dst_x += T::kXBytes; full += 8; empty += 8;
+      for (int tile = tile_first; tile < tile_end && ok; tile += tile_step) {
+        const int n_tile = tile % p.n_tiles;
+        const int m0 = (tile / p.n_tiles) * BLOCK_M;
+        const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
+        for (int kcoord = kb_begin * kBlockK; kcoord < kb_end * kBlockK; kcoord += kBlockK) {
+          ok = wait_bounded(empty, phase ^ 1, ctx, kStProducerEmpty);
+          if (!ok) break;
+          if (elect_one()) {
+            SK_TRACE_EVENT(0, issued);
+            mbar_arrive_expect_tx(full, kStageTxBytes);
+            bulk_load_1d(dst_wp, wsrc, kWpBytes, full);
+            tma_load_2d(dst_x, &tmap_x, kcoord, m0, full);
+          }
+          __syncwarp();
+          wsrc += kWpBytes; ++issued;
+          if (++stage == LSTAGES) {
+            stage = 0; phase ^= 1;
+            dst_wp = smem_base + T::kOffWp; dst_x = smem_base + T::kOffX; full = bar_ld_full; empty = bar_ld_empty;
+          } else {
+            dst_wp += kWpBytes; dst_x += T::kXBytes; full += 8; empty += 8;
+          }
         }
       }
       if (!ok) {
@@ -340,6 +395,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       bool ok = true;
       if (p.steps_per_group == 4) {
         // one K block == one scale group: four MMAs and three commits per iteration, nothing else
+        for (int tile = tile_first; tile < tile_end && ok; tile += tile_step)
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull) &&
                wait_bounded(bar_ex_full + 8 * e, eph, ctx, kStMmaExFull) &&
@@ -366,7 +422,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
             umma_commit(bar_acc_full + 8 * ab);
             umma_commit(bar_ld_empty + 8 * l);
             if constexpr (!T::kTied) umma_commit(bar_ex_empty + 8 * e);
-            SK_TRACE_EVENT(2, kb - kb_begin);
+            SK_TRACE_EVENT(2, SK_TRACE_BASE + kb - kb_begin);
           }
           __syncwarp();
 #ifdef SK_TRACE_MMA_LATENCY
@@ -382,6 +438,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       } else {
         // general group sizes (32, 64, 256, ...): track the position inside the group per 32-wide K step
         int pos = 0;
+        for (int tile = tile_first; tile < tile_end && ok; tile += tile_step)
         for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
           ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull) &&
                wait_bounded(bar_ex_full + 8 * e, eph, ctx, kStMmaExFull);
@@ -445,12 +502,16 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         wx_off[rr] = T::kOffWx + row * 128 + ((row & 7) << 4);
         wp_off[rr] = T::kOffWp + row * 16 + half * 2048;
       }
+      bool ok = true;
+      for (int tile = tile_first; tile < tile_end && ok; tile += tile_step)
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         // The loads below must not be issued before the wait has been seen to succeed: a load that does not depend
         // on the poll's predicate can be served before the barrier state is sampled and return stale bytes.
-        if (!wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStExpanderFull)) break;
+        ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStExpanderFull);
+        if (!ok) break;
         if constexpr (!T::kTied) {
-          if (!wait_bounded(bar_ex_empty + 8 * e, eph ^ 1, ctx, kStExpanderEmpty)) break;
+          ok = wait_bounded(bar_ex_empty + 8 * e, eph ^ 1, ctx, kStExpanderEmpty);
+          if (!ok) break;
         }
         const uint32_t wp = smem_base + wp_off[0] + l * kWpBytes;
         const uint4 q0 = ld_shared_v4(wp);
@@ -493,7 +554,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ex_full + 8 * e);
-        if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, kb - kb_begin);
+        if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, SK_TRACE_BASE + kb - kb_begin);
         if (++l == LSTAGES) { l = 0; lph ^= 1; }
         if (++e == ESTAGES) { e = 0; eph ^= 1; }
       }
@@ -505,17 +566,11 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane;      // output feature within the tile == TMEM lane
     const int col0 = wg * kCols;                 // first token column of this thread
-    const int n = n0 + row;
-    const bool n_ok = n < p.N;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + col0;
     const float kScaleUp = 1.2676506002282294e30f;     // 2^100
     const float bias_f = __uint_as_float(bias);        // bias * 2^-149
 
-    float acc[kCols];
-#pragma unroll
-    for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
-
-    // pre-set every accumulator buffer to the bias (once per tile) and hand them to the MMA issuer
+    // pre-set every accumulator buffer to the bias and hand them to the MMA issuer
 #pragma unroll
     for (int a = 0; a < ACC_BUFS; ++a) {
 #pragma unroll
@@ -528,29 +583,57 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
 #pragma unroll
       for (int a = 0; a < ACC_BUFS; ++a) mbar_arrive(bar_acc_empty + 8 * a);
     }
+    int ab = 0, tile_parity = 0;
+    uint32_t aph = 0;
+    bool epi_ok = true;
 
-    // group scales s_g .. s_{g+ACC_BUFS} in a register ring, loaded ACC_BUFS groups ahead (0 past the end).
-    // The ring keeps the raw fp16 bits: converting at load time would stall on the global load right away.
+    for (int tile = tile_first; tile < tile_end && epi_ok; tile += tile_step) {
+    const int n0 = (tile % p.n_tiles) * kTileN;
+    const int m0 = (tile / p.n_tiles) * BLOCK_M;
+    const int n = n0 + row;
+    const bool n_ok = n < p.N;
+    const bool more_tiles = PERSIST && tile + tile_step < tile_end;   // the buffers must be pre-set again for the next tile
+
+    float acc[kCols];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+    float* xs_tile = reinterpret_cast<float*>(smem + T::kOffXs) + (tile_parity ? BLOCK_M : 0);
+    if constexpr (PERSIST) {
+      // x_scale * 2^49 of this tile's tokens; read after the named barrier that precedes the output.  The buffer
+      // of the tile before last is free: every epilogue thread passed that tile's barrier before it got here.
+      for (int j = threadIdx.x; j < BLOCK_M; j += T::kEpiThreads)
+        xs_tile[j] = (m0 + j < p.M) ? __ldg(p.x_scale + m0 + j) * 5.62949953421312e14f : 0.f;
+      tile_parity ^= 1;
+    }
+
+    // group scales s_g .. s_{g+ACC_BUFS} in a register ring, loaded one group ahead of their first use (0 past the
+    // end).  The ring keeps the raw fp16 bits: converting at load time would stall on the global load right away.
+    // A load that misses L2 would still stall the loop one group later (the ring is shifted by register moves), so
+    // every row is pulled into L2 kScalePrefetchGroups groups earlier with a prefetch, which occupies no register.
     const unsigned short* sp =
         reinterpret_cast<const unsigned short*>(p.w_scale) + static_cast<size_t>(g_begin) * p.N + (n_ok ? n : 0);
     int g_load = g_begin;                       // next group whose scale is fetched
     auto load_scale = [&]() -> unsigned short {
       const unsigned short r = (n_ok && g_load < g_end) ? __ldg(sp) : static_cast<unsigned short>(0);
+#ifndef SK_NO_SCALE_PREFETCH
+      if (g_load + kScalePrefetchGroups < g_end)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + static_cast<size_t>(kScalePrefetchGroups) * p.N));
+#endif
       sp += p.N; ++g_load;
       return r;
     };
+    for (int i = ACC_BUFS + 1; i < kScalePrefetchGroups && g_begin + i < g_end; ++i)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + static_cast<size_t>(i) * p.N));
     unsigned short sr[ACC_BUFS + 1];
 #pragma unroll
     for (int i = 0; i <= ACC_BUFS; ++i) sr[i] = load_scale();
     float s_sum = 0.f;   // sum of the coefficients since the last bias flush
-    int ab = 0, flush = 0;
-    uint32_t aph = 0;
+    int flush = 0;
     // TMEM loads are software-pipelined across chunks AND groups: while chunk c is consumed the load of the
     // next chunk -- or of the first chunk of the next group -- is already in flight.
     constexpr bool kPipelined = false;   // cross-group prefetch costs more registers than the epilogue has
     constexpr int kBufMask = T::kDoubleBuf ? 1 : 0;
     uint32_t v[kBufMask + 1][kChunk];
-    bool epi_ok = true;
     if constexpr (kPipelined) {
       if (g_begin < g_end) {
         epi_ok = wait_bounded(bar_acc_full, 0, ctx, kStEpilogueAccFull);
@@ -566,9 +649,12 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       for (int i = 0; i < ACC_BUFS; ++i) sr[i] = sr[i + 1];
       sr[ACC_BUFS] = load_scale();
       const uint32_t buf = lane_addr + ab * BLOCK_M;
+      // the last groups of a tile keep their buffers until these are back at the bias for the next tile (below)
+      const bool keep_buf = more_tiles && g >= g_end - ACC_BUFS;
       if constexpr (!kPipelined) {
         if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 0);
-        if (!wait_bounded(bar_acc_full + 8 * ab, aph, ctx, kStEpilogueAccFull)) break;
+        epi_ok = wait_bounded(bar_acc_full + 8 * ab, aph, ctx, kStEpilogueAccFull);
+        if (!epi_ok) break;
         if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 1);
         tcgen05_fence_after_sync();
         if constexpr (T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf, v[0]);
@@ -590,7 +676,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
             tmem_ld_chunk<kChunk>(lane_addr + ab_next * BLOCK_M, v[0]);   // harmless if the wait gave up
           }
         }
-        if (c == kNumChunks - 1) {   // buffer fully read: hand it back to the MMA issuer (it keeps accumulating)
+        if (c == kNumChunks - 1 && !keep_buf) {   // buffer fully read: hand it back to the MMA issuer (it keeps accumulating)
           tcgen05_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
@@ -610,7 +696,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         for (int j = 0; j < kChunk; ++j)
           acc[c * kChunk + j] = fmaf(s2, __uint_as_float(v[c & kBufMask][j]), acc[c * kChunk + j]);
       }
-      if (threadIdx.x == 0) SK_TRACE_EVENT(3, g - g_begin);
+      if (threadIdx.x == 0) SK_TRACE_EVENT(3, SK_TRACE_BASE + g - g_begin);
       s_sum += s2;
       if (++flush == kBiasFlushGroups) {
         const float corr = s_sum * bias_f;
@@ -619,6 +705,26 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         s_sum = 0.f; flush = 0;
       }
       ab = ab_next; aph = aph_next;
+    }
+    if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 0);
+    if (more_tiles && epi_ok) {
+      // back to the bias for the next tile: the buffers of the last ACC_BUFS groups (all of them, if the tile had
+      // fewer groups: the untouched ones are at the bias already), then hand them to the MMA issuer
+      const int used = (g_end - g_begin) < ACC_BUFS ? (g_end - g_begin) : ACC_BUFS;
+      int b = ab;
+      for (int i = 0; i < used; ++i) {
+        b = (b == 0) ? ACC_BUFS - 1 : b - 1;
+#pragma unroll
+        for (int cc = 0; cc < kNumChunks; ++cc) tmem_fill_chunk<kChunk>(lane_addr + b * BLOCK_M + cc * kChunk, bias);
+      }
+      tmem_st_wait();
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      b = ab;
+      for (int i = 0; i < used; ++i) {
+        b = (b == 0) ? ACC_BUFS - 1 : b - 1;
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);
+      }
     }
     {
       const float corr = s_sum * bias_f;
@@ -629,6 +735,50 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
     // ---------------------------------------------------------------- output
     if constexpr (!DUMP) {
       const float kScaleDown = 5.62949953421312e14f;   // 2^49: acc holds (sum_g s P) * 2^-49
+      if constexpr (PERSIST) {
+        // Straight from the registers: a warp writes 32 consecutive features (64 bytes) of one token per store.
+        // The shared-memory ring is busy with the next tile, whose MMAs run while these stores are issued.
+        // The token scales were staged in shared memory at the start of the tile (two buffers, by tile parity).
+        // Each warpgroup sends its tokens in rounds of kStageTokens through its own staging buffer: convert and
+        // transpose into [token][feature], then one thread issues a TMA store (which clips at the edges of the
+        // output) and the warpgroup goes on; the buffer is reused once that store has read it.
+        if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 1);
+        named_barrier_sync(1, T::kEpiThreads);
+        if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 2);
+        const float* xs = xs_tile + col0;
+        const uint32_t stage_addr = smem_base + T::kOffStage + wg * T::kStageBytes;
+        uint16_t* stage = reinterpret_cast<uint16_t*>(smem + T::kOffStage + wg * T::kStageBytes);
+        const bool leader = (threadIdx.x & 127) == 0;
+#pragma unroll
+        for (int r = 0; r < kCols / T::kStageTokens; ++r) {
+          if (leader) bulk_wait_group_read0();
+          named_barrier_sync(2 + wg, 128);
+          if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 3 + 4 * r);
+          if (p.out_bf16) stage_tokens<T::kStageTokens, true>(acc, r * T::kStageTokens, xs + r * T::kStageTokens, stage + row);
+          else stage_tokens<T::kStageTokens, false>(acc, r * T::kStageTokens, xs + r * T::kStageTokens, stage + row);
+          if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 4 + 4 * r);
+          fence_proxy_async_smem();
+          named_barrier_sync(2 + wg, 128);
+          if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 5 + 4 * r);
+          if (leader) {
+            tma_store_2d(&tmap_out, n0, m0 + col0 + r * T::kStageTokens, stage_addr);
+            bulk_commit_group();
+          }
+          if (threadIdx.x == 0 && tile == tile_first) SK_TRACE_EVENT(6, 6 + 4 * r);
+          // further destinations (peer GPUs): plain 16-byte stores out of the staging buffer
+          for (int d = 0; d < p.n_extra; ++d) {
+            uint16_t* outp = reinterpret_cast<uint16_t*>(p.out_extra[d]);
+            for (int idx = threadIdx.x & 127; idx < T::kStageTokens * 16; idx += 128) {
+              const int jj = idx >> 4, ch = idx & 15;
+              const int m = m0 + col0 + r * T::kStageTokens + jj;
+              if (m < p.M)
+                *reinterpret_cast<uint4*>(outp + static_cast<size_t>(m) * p.ld_out + n0 + ch * 8) =
+                    *reinterpret_cast<const uint4*>(stage + jj * kTileN + ch * 8);
+            }
+          }
+        }
+        continue;
+      }
       // The operand ring is dead once the last group has been read (all MMAs and all TMA loads are complete):
       // reuse it to transpose the tile.  All epilogue threads must be past their last TMEM read first.
       float* xs_s = reinterpret_cast<float*>(smem + T::kOffXs);
@@ -638,13 +788,8 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
       if (threadIdx.x == 0) SK_TRACE_EVENT(4, 2);
       if (num_splits == 1) {
         uint16_t* st = reinterpret_cast<uint16_t*>(smem);   // [BLOCK_M][128] in the output dtype
-#pragma unroll
-        for (int j = 0; j < kCols; ++j) {
-          if ((j & 15) == 0) asm volatile("" ::: "memory");   // keep the scale loads from being hoisted en bloc
-          const float y = acc[j] * xs_s[col0 + j];
-          st[(col0 + j) * kTileN + row] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
-                                                     : __half_as_ushort(__float2half_rn(y));
-        }
+        if (p.out_bf16) stage_tokens<kCols, true>(acc, 0, xs_s + col0, st + col0 * kTileN + row);
+        else stage_tokens<kCols, false>(acc, 0, xs_s + col0, st + col0 * kTileN + row);
         named_barrier_sync(1, T::kEpiThreads);
         // destination 0 is this GPU's buffer; the others are peer-mapped buffers of the other ranks (plain
         // stores over NVLink, so the all-gather of the output overlaps the GEMM tile by tile)
@@ -675,6 +820,10 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         for (int j = 0; j < kCols; ++j) red[(col0 + j) * kTileN + row] = acc[j];
       }
     }
+    }   // tiles
+    if constexpr (PERSIST) {
+      if ((threadIdx.x & 127) == 0) bulk_wait_group0();   // this thread's TMA stores are complete
+    }
   }
 
   if constexpr (!DUMP) {
@@ -688,6 +837,8 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p)
         const uint32_t my_rank = cluster_ctarank();
         const int row = threadIdx.x & 127;
         const int wg = warp >> 2;
+        const int n0 = (tile_first % p.n_tiles) * kTileN;      // split-K CTAs own exactly one tile
+        const int m0 = (tile_first / p.n_tiles) * BLOCK_M;
         const int n = n0 + row;
         uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
         // token rows are dealt round-robin to (cluster rank, epilogue warpgroup); every remote load of a row

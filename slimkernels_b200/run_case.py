@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--token-tile", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--persistent", type=int, default=0, help="0 auto, 1 one CTA per tile, 2 resident CTAs walk the tiles")
     ap.add_argument("--weight-copies", type=int, default=1, help="cycle this many distinct weight buffers")
     args = ap.parse_args()
     load_extension()
@@ -39,6 +40,7 @@ def main() -> None:
         plan = W2A8Plan(wp, ws, group_size=G)
         plan.set_option(capi.SK_OPT_TOKEN_TILE, args.token_tile)
         plan.set_option(capi.SK_OPT_SPLIT_K, args.split_k)
+        plan.set_option(capi.SK_OPT_PERSISTENT, args.persistent)
         plans.append(plan)
     x_q = torch.from_numpy(rng.integers(-127, 128, size=(M, K), dtype=np.int8)).to(dev)
     xs = torch.from_numpy(rng.uniform(0.005, 0.02, size=(M,)).astype(np.float32)).to(dev)

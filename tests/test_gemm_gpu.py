@@ -78,6 +78,24 @@ def test_every_tile_and_split(token_tile, split_k):
     _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, split_k=split_k))
 
 
+@pytest.mark.parametrize("token_tile,M,N,K,G", [
+    (128, 1000, 2400, 384, 128),    # 8 x 19 = 152 tiles > 148 SMs: some CTAs walk two tiles, ragged edges
+    (256, 2000, 2400, 384, 128),
+    (128, 2304, 2432, 320, 64),     # 342 tiles, groups spanning half a K block, 5 groups per tile (odd)
+    (256, 4600, 2176, 128, 128),    # one group per tile: fewer groups than accumulator buffers
+])
+def test_persistent_tile_walk(token_tile, M, N, K, G):
+    """More tiles than SMs: a resident set of CTAs walks the tiles; bit-identical to one CTA per tile."""
+    x_q, xs, wp, ws = random_problem(M, N, K, G, seed=token_tile + M)
+    dp = DeviceProblem(x_q, xs, wp, ws, group_size=G)
+    y_one = to_np(dp.force(token_tile=token_tile, persistent=1).gemm())
+    y_walk = to_np(dp.force(token_tile=token_tile, persistent=2).gemm())
+    y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp, ws, group_size=G)
+    assert np.abs(y_walk - y_ref).max() <= TOL
+    assert np.array_equal(y_walk, y_one)
+    assert np.array_equal(y_walk, to_np(dp.gemm()))   # and again: nothing left over from the first launch
+
+
 @pytest.mark.parametrize("M,N,K,G", [
     (1, 128, 128, 128), (1, 8, 32, 32), (7, 130, 256, 128), (33, 200, 384, 128), (5, 136, 352, 32),
     (16, 264, 512, 64), (9, 128, 768, 256), (129, 257, 1408, 128), (300, 1000, 640, 128),
