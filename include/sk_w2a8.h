@@ -57,7 +57,8 @@ typedef enum sk_weight_layout {
 
 /* Keys of sk_w2a8_set_option (testing / tuning; 0 or SK_AUTO restores the heuristic). */
 typedef enum sk_option {
-  SK_OPT_KERNEL = 1,      /* 0 auto, 1 tcgen05 kernel, 2 CUDA-core checker kernel (needs SK_WEIGHT_ROWMAJOR) */
+  SK_OPT_KERNEL = 1,      /* 0 auto, 1 general tcgen05 kernel, 2 CUDA-core checker kernel (needs SK_WEIGHT_ROWMAJOR),
+                             3 decode tcgen05 kernel (group size 128; used for token tiles 16 / 32, else 1 is taken) */
   SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 / 192 / 256 */
   SK_OPT_SPLIT_K = 3,     /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
   SK_OPT_PERSISTENT = 4   /* 0 auto (= 1), 1 one CTA per tile, 2 one resident set of CTAs walks all tiles (token tiles

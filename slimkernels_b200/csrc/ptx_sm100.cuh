@@ -261,6 +261,10 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
   return v;
 }
 
+__device__ __forceinline__ void st_dsmem_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {   // volatile: may be re-issued after a wait
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)

@@ -12,6 +12,7 @@
 
 #include "activation.cuh"
 #include "w2a8_umma.cuh"
+#include "w2a8_decode.cuh"
 
 namespace sk {
 
@@ -181,7 +182,7 @@ static long long* g_trace_buffer = nullptr;
 #endif
 
 struct LaunchChoice {
-  int kernel;      // 1 tcgen05, 2 CUDA-core checker
+  int kernel;      // 1 tcgen05 (general), 2 CUDA-core checker, 3 tcgen05 (decode: token tiles 16 / 32, group size 128)
   int token_tile;  // 16 / 32 / 64 / 128
   int split_k;     // 1 / 2 / 4 / 8
   int persistent;  // 1: one resident set of CTAs walks all tiles
@@ -190,19 +191,23 @@ struct LaunchChoice {
 
 static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   LaunchChoice c;
-  c.kernel = plan->opt_kernel ? plan->opt_kernel : 1;
   if (plan->opt_token_tile) c.token_tile = plan->opt_token_tile;
   else c.token_tile = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const bool decode_ok = plan->G == 128 && c.token_tile <= 32;
+  c.kernel = plan->opt_kernel ? plan->opt_kernel : (decode_ok ? 3 : 1);
+  if (c.kernel == 3 && !decode_ok) c.kernel = 1;
   const int groups = static_cast<int>(plan->K / plan->G);
   if (plan->opt_split_k) c.split_k = plan->opt_split_k;
   else {
     // Fill the machine in ONE wave: split the K range of a tile over a cluster while the CTAs still fit the
-    // resident capacity (2 CTAs per SM for token tiles <= 32, else 1) and every CTA keeps >= 4 groups.
+    // resident capacity (2 CTAs per SM for token tiles <= 32, else 1) and every CTA keeps enough groups to
+    // amortise its prologue (8 = two pipeline stages of the decode kernel, else 4).
     const long long tiles = plan->n_tiles * ((M + c.token_tile - 1) / c.token_tile);
     const long long capacity = static_cast<long long>(plan->sm_count) * (c.token_tile <= 32 ? 2 : 1);
+    const int min_groups = c.kernel == 3 ? 8 : 4;
     int s = 1;
     if (c.token_tile <= 64)
-      while (s < 8 && tiles * (2 * s) <= capacity && groups / (2 * s) >= 4) s *= 2;
+      while (s < 8 && tiles * (2 * s) <= capacity && groups / (2 * s) >= min_groups) s *= 2;
     c.split_k = s;
   }
   if (c.split_k > groups) c.split_k = 1;
@@ -250,16 +255,49 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtenso
   return SK_OK;
 }
 
+template <int TOK, bool DUMP>
+static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
+                         cudaStream_t stream) {
+  using L = DecodeTraits<TOK>;
+  auto kern = w2a8_decode_kernel<TOK, DUMP>;
+  static int configured_device_mask[64] = {0};
+  if (plan->device < 64 && !configured_device_mask[plan->device]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    if (e != cudaSuccess) return cuda_fail(plan, e);
+    configured_device_mask[plan->device] = 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan->n_tiles, m_tiles, split_k);
+  cfg.blockDim = dim3(L::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kDynamicBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (split_k > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = split_k;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, prm);
+  if (e != cudaSuccess) return cuda_fail(plan, e);
+  return SK_OK;
+}
+
 constexpr int kAccBufsSmall = 4;   // accumulator buffers of the token tiles <= 128
 constexpr int kAccBufs256 = 2;     // 2 x 256 columns fill the tensor memory
-static int acc_bufs_of(int token_tile) { return token_tile >= 192 ? kAccBufs256 : kAccBufsSmall; }
+static int acc_bufs_of(int token_tile, int kernel) {
+  if (kernel == 3) return token_tile == 16 ? DecodeTraits<16>::kAccBufs : DecodeTraits<32>::kAccBufs;
+  return token_tile >= 192 ? kAccBufs256 : kAccBufsSmall;
+}
 
 // The running sum of one accumulator buffer must stay inside (-2^22, 2^22):
 // (K handled per buffer) * 127 * max|code - zp| < 2^22.
-static bool running_sum_fits(const sk_w2a8_plan* plan, int token_tile, int split_k) {
+static bool running_sum_fits(const sk_w2a8_plan* plan, int token_tile, int split_k, int kernel) {
   const long long groups = plan->K / plan->G;
   const long long groups_cta = (groups + split_k - 1) / split_k;
-  const int ab = acc_bufs_of(token_tile);
+  const int ab = acc_bufs_of(token_tile, kernel);
   const long long k_per_buf = ((groups_cta + ab - 1) / ab) * plan->G;
   const int mx = plan->zero_point > 3 - plan->zero_point ? plan->zero_point : 3 - plan->zero_point;
   return k_per_buf * 127 * mx < (1LL << 22);
@@ -364,8 +402,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
   }
   LaunchChoice ch = choose(plan, M);
   if (partials) ch.split_k = 1;
-  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k)) {
-    if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1)) ch.token_tile = 128;
+  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k, ch.kernel)) {
+    if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1, 1)) ch.token_tile = 128;
     else return SK_ERR_BAD_SHAPE;   // K too deep for the int32 running sums of this tile configuration
   }
   int rc = SK_OK;
@@ -426,15 +464,21 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       }
       if (m_tiles > 65535) rc = SK_ERR_BAD_SHAPE;
       else if (partials) {
-        rc = dispatch_umma<true>(plan, ch.token_tile, map, out_map, prm, m_tiles, 1, 0, stream);
+        if (ch.kernel == 3)
+          rc = ch.token_tile == 16 ? launch_decode<16, true>(plan, map, prm, m_tiles, 1, stream)
+                                   : launch_decode<32, true>(plan, map, prm, m_tiles, 1, stream);
+        else rc = dispatch_umma<true>(plan, ch.token_tile, map, out_map, prm, m_tiles, 1, 0, stream);
         if (rc == SK_OK) {
           const long long mn = M * plan->N;
           const int blocks = static_cast<int>(mn / 256 + 1 < 148 * 8 ? mn / 256 + 1 : 148 * 8);
-          diff_partials_kernel<<<blocks, 256, 0, stream>>>(partials, prm.groups, mn, acc_bufs_of(ch.token_tile));
+          diff_partials_kernel<<<blocks, 256, 0, stream>>>(partials, prm.groups, mn, acc_bufs_of(ch.token_tile, ch.kernel));
           e = cudaGetLastError();
           if (e != cudaSuccess) rc = cuda_fail(plan, e);
         }
       }
+      else if (ch.kernel == 3)
+        rc = ch.token_tile == 16 ? launch_decode<16, false>(plan, map, prm, m_tiles, ch.split_k, stream)
+                                 : launch_decode<32, false>(plan, map, prm, m_tiles, ch.split_k, stream);
       else rc = dispatch_umma<false>(plan, ch.token_tile, map, out_map, prm, m_tiles, ch.split_k, persist ? ch.ctas : 0, stream);
     }
   }
@@ -597,8 +641,9 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
   if (!plan) return SK_ERR_NULL_POINTER;
   switch (key) {
     case SK_OPT_KERNEL:
-      if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
+      if (value < 0 || value > 3) return SK_ERR_BAD_ARGUMENT;
       if (value == 2 && !plan->w_rowmajor) return SK_ERR_UNAVAILABLE;
+      if (value == 3 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       plan->opt_kernel = static_cast<int>(value);
       return SK_OK;
     case SK_OPT_TOKEN_TILE:

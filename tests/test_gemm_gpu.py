@@ -78,6 +78,34 @@ def test_every_tile_and_split(token_tile, split_k):
     _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, split_k=split_k))
 
 
+@pytest.mark.parametrize("token_tile", [16, 32])
+@pytest.mark.parametrize("split_k", [1, 2, 4, 8])
+@pytest.mark.parametrize("K", [128, 640, 1408, 4096])
+def test_decode_kernel_every_tile_split_and_depth(token_tile, split_k, K):
+    """The decode kernel (four K blocks per stage, weights expanded into tensor memory): K-block counts that are
+    and are not multiples of its stage (1, 5, 11, 32), every cluster size, ragged M and N."""
+    if split_k > K // 128:
+        pytest.skip("more splits than groups")
+    M = {16: 13, 32: 29}[token_tile]
+    prob = random_problem(M, 392, K, 128, seed=token_tile + split_k + K)
+    _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05_DECODE, token_tile=token_tile, split_k=split_k))
+
+
+def test_decode_kernel_is_the_default_for_small_batches():
+    x_q, xs, wp, ws = random_problem(8, 512, 2048, 128, seed=3)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    assert dp.plan.query_launch(8)["kernel"] == capi.KERNEL_TCGEN05_DECODE
+    assert dp.plan.query_launch(64)["kernel"] == capi.KERNEL_TCGEN05
+    y = to_np(dp.gemm())
+    y_general = to_np(dp.force(kernel=capi.KERNEL_TCGEN05).gemm())
+    y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)
+    assert np.abs(y - y_ref).max() <= TOL and np.abs(y_general - y_ref).max() <= TOL
+    # several token tiles in one launch
+    x_q, xs, wp, ws = random_problem(61, 256, 1024, 128, seed=4)
+    dp = DeviceProblem(x_q, xs, wp, ws).force(kernel=capi.KERNEL_TCGEN05_DECODE, token_tile=16)
+    assert np.abs(to_np(dp.gemm()) - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+
+
 @pytest.mark.parametrize("token_tile,M,N,K,G", [
     (128, 1000, 2400, 384, 128),    # 8 x 19 = 152 tiles > 148 SMs: some CTAs walk two tiles, ragged edges
     (256, 2000, 2400, 384, 128),
