@@ -29,10 +29,12 @@ struct DecodeTraits {
   static_assert(TOK == 16 || TOK == 32, "token tile of the decode kernel");
   static constexpr int kKbPerStage = 4;                      // K blocks per load stage
   static constexpr int kStages = TOK == 16 ? 4 : 3;
-  static constexpr int kGroupsPerSet = 64 / TOK;             // scale groups (= K blocks) per accumulator set
+  static constexpr int kGroupsPerSet = 2;                    // scale groups (= K blocks) per accumulator set: a half stage
   static constexpr int kAccBufs = 2 * kGroupsPerSet;         // accumulator buffers: two sets
-  static constexpr int kACol0 = 128;                         // tensor memory: [0,128) accumulators, [128,256) weights
+  static constexpr int kAccCols = kAccBufs * TOK;            // tensor memory: [0, kAccCols) accumulators, then weights
+  static constexpr int kACol0 = kAccCols;
   static constexpr uint32_t kTmemCols = 256;
+  static constexpr int kASubs = (256 - kAccCols) / 64;       // half-stage buffers of expanded weights: 3 (16 tokens) or 2
   static constexpr int kXKbBytes = TOK * kBlockK;            // one activation box
   static constexpr int kStageWBytes = kKbPerStage * kWpBytes;
   static constexpr int kStageBytes = kStageWBytes + kKbPerStage * kXKbBytes;
@@ -45,7 +47,7 @@ struct DecodeTraits {
   static constexpr int kOffBar = kStages * kStageBytes + (kRedInRing ? 0 : TOK * kTileN * 4);
   static_assert(TOK * kTileN * 4 <= kStages * kStageBytes, "reduction buffer");
   static constexpr int kSubRing = 2 * kStages;               // ring of "MMAs of a half stage are complete" barriers
-  static constexpr int kNumBars = kStages + kSubRing + 4;
+  static constexpr int kNumBars = kStages + kSubRing + kASubs + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kTotal = kOffMisc + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;        // slack for 1024-byte alignment of the base
@@ -74,8 +76,8 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   // after its last half stage).  A commit costs the issuing thread a few hundred cycles, far more than the MMAs of a
   // decode-sized tile, so they are the currency to save.
   const uint32_t bar_sub_done = bar_ld_full + 8u * S;
-  const uint32_t bar_ex_full = bar_sub_done + 8u * T::kSubRing;   // [2] expanded weights of a half stage are in tensor memory
-  const uint32_t bar_acc_empty = bar_ex_full + 16u;               // [2] the epilogue has read the accumulator set
+  const uint32_t bar_ex_full = bar_sub_done + 8u * T::kSubRing;   // [kASubs] expanded weights of a half stage are in tensor memory
+  const uint32_t bar_acc_empty = bar_ex_full + 8u * T::kASubs;    // [2] the epilogue has read the accumulator set
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::kOffMisc + 4);
   const WaitCtx ctx{abort_flag, p.status};
@@ -99,7 +101,8 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) mbar_init(bar_ld_full + 8 * i, 1);
     for (int i = 0; i < T::kSubRing; ++i) mbar_init(bar_sub_done + 8 * i, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_ex_full + 8 * i, T::kExpWarps); mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps); }
+    for (int i = 0; i < T::kASubs; ++i) mbar_init(bar_ex_full + 8 * i, T::kExpWarps);
+    for (int i = 0; i < 2; ++i) mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -156,17 +159,15 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     // ============================================================ MMA issuer (whole warp loops, one lane issues)
     constexpr uint32_t idesc = make_idesc_i8(kTileN, TOK, /*a_signed=*/true, /*b_signed=*/true);
     const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_base + T::kStageWBytes);
-    int stage = 0;
-    uint32_t lph = 0;
+    int stage = 0, a = 0;                       // load stage; tensor-memory buffer of expanded weights
+    uint32_t lph = 0, eph = 0;
     bool ok = true;
     const int num_subs = (nkb + 1) >> 1;
-    for (int u = 0; u < num_subs; ++u) {        // one half stage (two K blocks, eight MMAs) per iteration
+    for (int u = 0; u < num_subs; ++u) {        // one half stage (two K blocks, eight MMAs, one accumulator set)
       const int i0 = 2 * u;
-      const int a = u & 1;                      // tensor-memory buffer of expanded weights
-      const int si = i0 / GS;                   // accumulator set counter
-      if (a == 0) ok = wait_bounded(bar_ld_full + 8 * stage, lph, ctx, kStMmaLdFull);
-      if (ok) ok = wait_bounded(bar_ex_full + 8 * a, (u >> 1) & 1, ctx, kStMmaExFull);
-      if (ok && i0 % GS == 0) ok = wait_bounded(bar_acc_empty + 8 * (si & 1), (si >> 1) & 1, ctx, kStMmaAccEmpty);
+      if ((u & 1) == 0) ok = wait_bounded(bar_ld_full + 8 * stage, lph, ctx, kStMmaLdFull);
+      if (ok) ok = wait_bounded(bar_ex_full + 8 * a, eph, ctx, kStMmaExFull);
+      if (ok) ok = wait_bounded(bar_acc_empty + 8 * (u & 1), (u >> 1) & 1, ctx, kStMmaAccEmpty);
       if (!ok) break;
       tcgen05_fence_after_sync();
       if (elect_one()) {
@@ -186,7 +187,8 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
         SK_TRACE_EVENT(2, u);
       }
       __syncwarp();
-      if (a == 1 && ++stage == S) { stage = 0; lph ^= 1; }
+      if ((u & 1) && ++stage == S) { stage = 0; lph ^= 1; }
+      if (++a == T::kASubs) { a = 0; eph ^= 1; }
     }
     __syncwarp();
   } else if (warp >= kExpWarp0 && warp < kProducerWarp) {
@@ -196,17 +198,16 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     const uint32_t lut = (static_cast<uint32_t>(0 - zp) & 0xffu) | ((static_cast<uint32_t>(1 - zp) & 0xffu) << 8) |
                          ((static_cast<uint32_t>(2 - zp) & 0xffu) << 16) | ((static_cast<uint32_t>(3 - zp) & 0xffu) << 24);
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + T::kACol0;
-    int stage = 0;
+    int stage = 0, a = 0;
     uint32_t lph = 0;
     bool ok = true;
     for (int i = 0; i < nkb && ok; i += 2) {
-      const int a = (i >> 1) & 1;
       if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(6, (i >> 1) * 8 + 0);
       // The loads below must not be issued before the waits have been seen to succeed: a load that does not depend
       // on the poll's predicate can be served before the barrier state is sampled and return stale bytes.
       if ((i & 3) == 0) ok = wait_bounded(bar_ld_full + 8 * stage, lph, ctx, kStExpanderFull);
-      if (ok && i >= 4) {   // the buffer is free once the MMAs of the half stage before last are complete
-        const int u = (i >> 1) - 2;
+      if (ok && (i >> 1) >= T::kASubs) {   // the buffer is free once the MMAs that read its previous contents are complete
+        const int u = (i >> 1) - T::kASubs;
         ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStExpanderEmpty);
       }
       if (!ok) break;
@@ -234,6 +235,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       if (lane == 0) mbar_arrive(bar_ex_full + 8 * a);
       if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, i >> 1);
       if ((i & 3) == 2 && ++stage == S) { stage = 0; lph ^= 1; }
+      if (++a == T::kASubs) a = 0;
     }
   } else if (warp < T::kEpiWarps) {
     // ============================================================ epilogue: TMEM lane = output feature
@@ -247,7 +249,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 
     // pre-set the accumulator columns to the bias (once) and hand both sets to the MMA issuer
 #pragma unroll
-    for (int c = 0; c < 128; c += 32) tmem_st_fill_32x32(lane_addr + c, bias);
+    for (int c = 0; c < T::kAccCols; c += 32) tmem_st_fill_32x32(lane_addr + c, bias);
     tmem_st_wait();
     tcgen05_fence_before_sync();
     __syncwarp();
@@ -288,19 +290,18 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     const int num_sets = (nkb + GS - 1) / GS;
     for (int si = 0; si < num_sets; ++si) {
       coeffs(si + 1, c_next);      // zeros past the end
-      {   // the set is complete when the MMAs of its last half stage are
-        const int u = min((((si + 1) * GS - 1) >> 1), ((nkb + 1) >> 1) - 1);
-        ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStEpilogueAccFull);
-      }
+      // set si is complete when the MMAs of half stage si are
+      ok = wait_bounded(bar_sub_done + 8 * (si % T::kSubRing), (si / T::kSubRing) & 1, ctx, kStEpilogueAccFull);
       if (!ok) break;
       tcgen05_fence_after_sync();
-      constexpr int kGroupsPerHalf = 32 / TOK;     // a set is read in two loads of 32 columns
+      constexpr int kLoadsPerSet = GS * TOK / 32;   // a set is read in loads of 32 columns
+      constexpr int kGroupsPerHalf = 32 / TOK;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < kLoadsPerSet; ++h) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + (si & 1) * 64 + h * 32, v);
+        tmem_ld_32x32(lane_addr + (si & 1) * (GS * TOK) + h * 32, v);
         tmem_ld_wait();
-        if (h == 1) {
+        if (h == kLoadsPerSet - 1) {
           tcgen05_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_acc_empty + 8 * (si & 1));   // the MMAs keep accumulating into the set
