@@ -243,6 +243,24 @@ __device__ __forceinline__ void stage_tokens(const float (&acc)[NACC], int j0, c
   }
 }
 
+// Tile order.  CTAs are handed out in the order of their linear tile number, so tiles that run at the same time
+// should share operands in L2: tiles are numbered in bands of kBandTiles token tiles, feature tile by feature tile
+// inside a band.  The ~148 tiles in flight then read few feature tiles' weights (each reused by the whole band)
+// and kBandTiles token tiles' activations, instead of streaming the whole weight matrix once per token tile.
+constexpr int kBandTiles = 4;
+struct TileCoord { int n_tile, m_tile; };
+__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tiles, int num_tiles) {
+  const int m_tiles = num_tiles / n_tiles;
+  const int per_band = kBandTiles * n_tiles;
+  const int band = tile / per_band;
+  const int r = tile - band * per_band;
+  const int h = min(kBandTiles, m_tiles - band * kBandTiles);   // token tiles in this band (the last may be short)
+  TileCoord c;
+  c.n_tile = r / h;
+  c.m_tile = band * kBandTiles + (r - c.n_tile * h);
+  return c;
+}
+
 template <int CHUNK>
 __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&v)[CHUNK]) {
   if constexpr (CHUNK == 32) tmem_ld_32x32(taddr, v); else tmem_ld_32x16(taddr, v);
@@ -349,8 +367,9 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = tile_first; tile < tile_end && ok; tile += tile_step) {
-        const int n_tile = tile % p.n_tiles;
-        const int m0 = (tile / p.n_tiles) * BLOCK_M;
+        const TileCoord tc = tile_coord(tile, p.n_tiles, p.num_tiles);
+        const int n_tile = tc.n_tile;
+        const int m0 = tc.m_tile * BLOCK_M;
         const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
         for (int kcoord = kb_begin * kBlockK; kcoord < kb_end * kBlockK; kcoord += kBlockK) {
           ok = wait_bounded(empty, phase ^ 1, ctx, kStProducerEmpty);
@@ -588,8 +607,9 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     bool epi_ok = true;
 
     for (int tile = tile_first; tile < tile_end && epi_ok; tile += tile_step) {
-    const int n0 = (tile % p.n_tiles) * kTileN;
-    const int m0 = (tile / p.n_tiles) * BLOCK_M;
+    const TileCoord tc = tile_coord(tile, p.n_tiles, p.num_tiles);
+    const int n0 = tc.n_tile * kTileN;
+    const int m0 = tc.m_tile * BLOCK_M;
     const int n = n0 + row;
     const bool n_ok = n < p.N;
     const bool more_tiles = PERSIST && tile + tile_step < tile_end;   // the buffers must be pre-set again for the next tile
@@ -837,8 +857,9 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const uint32_t my_rank = cluster_ctarank();
         const int row = threadIdx.x & 127;
         const int wg = warp >> 2;
-        const int n0 = (tile_first % p.n_tiles) * kTileN;      // split-K CTAs own exactly one tile
-        const int m0 = (tile_first / p.n_tiles) * BLOCK_M;
+        const TileCoord tc = tile_coord(tile_first, p.n_tiles, p.num_tiles);   // split-K CTAs own exactly one tile
+        const int n0 = tc.n_tile * kTileN;
+        const int m0 = tc.m_tile * BLOCK_M;
         const int n = n0 + row;
         uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
         // token rows are dealt round-robin to (cluster rank, epilogue warpgroup); every remote load of a row
