@@ -385,42 +385,41 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 
   if constexpr (!DUMP) {
     if (num_splits > 1) {
-      // split-K: fixed-order reduction over the cluster through distributed shared memory
+      // split-K: fixed-order reduction over the cluster through distributed shared memory.
+      // Every thread of the CTA helps: the CTA owns TOK / num_splits token rows of 128 features, and slot
+      // k * num_splits + r of the buffer holds rank r's partial sum of row my_rank + k * num_splits.
       const float kScaleDown = 5.62949953421312e14f;
+      const int my_rank = static_cast<int>(cluster_ctarank());
+      const int rows = TOK / num_splits;
+      constexpr int kMaxIter = (TOK / 2 * kTileN + T::kThreads - 1) / T::kThreads;
+      float xs[kMaxIter];     // the token scales of this thread's outputs, fetched before the barrier
+#pragma unroll
+      for (int it = 0; it < kMaxIter; ++it) {
+        const int idx = threadIdx.x + it * T::kThreads;
+        const int m = m0 + my_rank + (idx >> 7) * num_splits;
+        xs[it] = (idx < rows * kTileN && m < p.M) ? __ldg(p.x_scale + m) * kScaleDown : 0.f;
+      }
       __syncwarp();
       cluster_sync_all();
       if (threadIdx.x == 0) SK_TRACE_EVENT(4, 5);
-      if (warp < T::kEpiWarps) {
+      {
         const float* red = reinterpret_cast<const float*>(smem + T::kOffRed);
-        const int my_rank = static_cast<int>(cluster_ctarank());
-        const int row = threadIdx.x & 127;
-        const int n = n0 + row;
-        const int sh = num_splits == 2 ? 1 : num_splits == 4 ? 2 : 3;
-        // slot q = k * num_splits + r holds rank r's partial sum of token row my_rank + k * num_splits;
-        // the sums run in rank order (deterministic)
-        // (all loads before the first store: the compiler cannot move a load above a store that might alias it)
-        float part[TOK], xs[TOK];
 #pragma unroll
-        for (int q = 0; q < TOK; ++q) {
-          const int m = m0 + my_rank + ((q >> sh) << sh);
-          part[q] = red[q * kTileN + row];
-          xs[q] = ((q & (num_splits - 1)) == 0 && m < p.M) ? __ldg(p.x_scale + m) * kScaleDown : 0.f;
-        }
-        float sum = 0.f, xs_row = 0.f;
-#pragma unroll
-        for (int q = 0; q < TOK; ++q) {
-          const int r = q & (num_splits - 1);
-          if (r == 0) { sum = part[q]; xs_row = xs[q]; } else sum += part[q];
-          if (r == num_splits - 1) {
-            const int m = m0 + my_rank + ((q >> sh) << sh);
-            if (m < p.M && n < p.N) {
-              const float y = sum * xs_row;
-              const uint16_t bits = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
-                                               : __half_as_ushort(__float2half_rn(y));
-              reinterpret_cast<uint16_t*>(p.out)[static_cast<size_t>(m) * p.ld_out + n] = bits;
-              for (int d = 0; d < p.n_extra; ++d)
-                reinterpret_cast<uint16_t*>(p.out_extra[d])[static_cast<size_t>(m) * p.ld_out + n] = bits;
-            }
+        for (int it = 0; it < kMaxIter; ++it) {
+          const int idx = threadIdx.x + it * T::kThreads;
+          const int k = idx >> 7, row = idx & 127;
+          const int m = m0 + my_rank + k * num_splits;
+          const int n = n0 + row;
+          if (idx < rows * kTileN && m < p.M && n < p.N) {
+            const float* src = red + (k * num_splits) * kTileN + row;
+            float sum = src[0];
+            for (int r = 1; r < num_splits; ++r) sum += src[r * kTileN];   // rank order: deterministic
+            const float y = sum * xs[it];
+            const uint16_t bits = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
+                                             : __half_as_ushort(__float2half_rn(y));
+            reinterpret_cast<uint16_t*>(p.out)[static_cast<size_t>(m) * p.ld_out + n] = bits;
+            for (int d = 0; d < p.n_extra; ++d)
+              reinterpret_cast<uint16_t*>(p.out_extra[d])[static_cast<size_t>(m) * p.ld_out + n] = bits;
           }
         }
       }
