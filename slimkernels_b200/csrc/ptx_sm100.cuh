@@ -276,6 +276,12 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
                : "memory");
 }
 
+// Programmatic dependent launch.  launch_dependents: the next kernel in the stream (if it was launched with the
+// programmatic-serialization attribute) may start being scheduled now; wait: every kernel this one depends on has
+// completed and its memory is visible.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // named barrier among a subset of warps (id 1..15)
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

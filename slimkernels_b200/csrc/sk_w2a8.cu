@@ -164,7 +164,7 @@ struct sk_w2a8_plan {
   const __half* w_scale = nullptr;      // borrowed
   int* status = nullptr;                // device, owned
   int last_cuda_error = 0;
-  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0;
+  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0, opt_pdl = 0;
   std::vector<sk::CachedMap> maps;      // small cache of activation tensor maps
   std::mutex mu;
 };
@@ -271,15 +271,24 @@ static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmP
   cfg.blockDim = dim3(L::kThreads, 1, 1);
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int na = 0;
   if (split_k > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = split_k;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = split_k;
+    ++na;
   }
+  if (!DUMP && plan->opt_pdl != 1) {
+    // programmatic dependent launch: this kernel's set-up may overlap the tail of the previous kernel in the stream
+    // (the kernel itself waits for that kernel before it touches activations or outputs)
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, prm);
   if (e != cudaSuccess) return cuda_fail(plan, e);
   return SK_OK;
@@ -654,6 +663,10 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
     case SK_OPT_SPLIT_K:
       if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return SK_ERR_BAD_ARGUMENT;
       plan->opt_split_k = static_cast<int>(value);
+      return SK_OK;
+    case SK_OPT_DEPENDENT_LAUNCH:
+      if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_pdl = static_cast<int>(value);
       return SK_OK;
     case SK_OPT_PERSISTENT:
       if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;

@@ -116,15 +116,49 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) SK_TRACE_EVENT(4, 1);
+  // Programmatic dependent launch: the next kernel in the stream may be scheduled as soon as this CTA gets here, and
+  // this kernel may itself have started before the previous one finished.  Weights and group scales are constants,
+  // so the copies of the first stages' weights go out at once; every thread that reads activations or token scales
+  // or writes outputs waits for the previous kernel first (grid_dep_wait below).
+  grid_dep_launch_dependents();
 
   if (warp == kProducerWarp) {
     // ============================================================ producer (whole warp loops, one lane issues)
     const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
     int stage = 0, issued = 0;
     bool ok = true;
-    for (int i = 0; i < nkb; i += T::kKbPerStage) {
+    // first round of stages: the weight copies first (they depend on nothing), then, once the previous kernel in the
+    // stream is complete, the activation boxes
+    if (elect_one()) {
+      const uint8_t* w = wsrc;
+      for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
+        const int n = min(T::kKbPerStage, nkb - i);
+        const uint32_t full = bar_ld_full + 8 * st;
+        SK_TRACE_EVENT(0, st);
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(n) * (kWpBytes + T::kXKbBytes));
+        bulk_load_1d(smem_base + st * T::kStageBytes, w, static_cast<uint32_t>(n) * kWpBytes, full);
+        w += static_cast<size_t>(n) * kWpBytes;
+      }
+    }
+    __syncwarp();
+    grid_dep_wait();
+    if (elect_one()) {
+      for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
+        const int n = min(T::kKbPerStage, nkb - i);
+        for (int j = 0; j < n; ++j)
+          tma_load_2d(smem_base + st * T::kStageBytes + T::kStageWBytes + j * T::kXKbBytes, &tmap_x,
+                      (kb_begin + i + j) * kBlockK, m0, bar_ld_full + 8 * st);
+      }
+    }
+    __syncwarp();
+    for (int i = 0; i < nkb && issued < S; i += T::kKbPerStage) {
+      wsrc += static_cast<size_t>(min(T::kKbPerStage, nkb - i)) * kWpBytes;
+      ++issued;
+    }
+    // later rounds: a stage is refilled once the MMAs of its second half (of its previous use) are complete
+    for (int i = issued * T::kKbPerStage; i < nkb; i += T::kKbPerStage) {
       const int n = min(T::kKbPerStage, nkb - i);
-      if (issued >= S) {   // the stage is free once the MMAs of its second half (of its previous use) are complete
+      {
         const int u = 2 * (issued - S) + 1;
         ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStProducerEmpty);
         if (!ok) break;
@@ -341,6 +375,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 
     // ---------------------------------------------------------------- output
     if (threadIdx.x == 0) SK_TRACE_EVENT(4, 2);
+    grid_dep_wait();   // token scales and outputs belong to the stream's data flow
     if constexpr (!DUMP) {
       if (num_splits == 1) {
         // straight from the registers: a warp writes 32 consecutive features (64 bytes) of one token per store
@@ -389,6 +424,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       // Every thread of the CTA helps: the CTA owns TOK / num_splits token rows of 128 features, and slot
       // k * num_splits + r of the buffer holds rank r's partial sum of row my_rank + k * num_splits.
       const float kScaleDown = 5.62949953421312e14f;
+      grid_dep_wait();
       const int my_rank = static_cast<int>(cluster_ctarank());
       const int rows = TOK / num_splits;
       constexpr int kMaxIter = (TOK / 2 * kTileN + T::kThreads - 1) / T::kThreads;
