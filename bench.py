@@ -241,7 +241,9 @@ def decode_sweep(dev, peaks):
             gbs = wbytes / (ms_graph * 1e-3) / 1e9
             out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(us, 3), "gbs": round(gbs, 1),
                         "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "us_single_launch_l2_warm": round(ms_single * 1e3, 3),
-                        "weight_copies": ncopies, "algorithmic_bytes": wbytes})
+                        "weight_copies": ncopies, "algorithmic_bytes": wbytes,
+                        "kernel": "w2a8_decode_kernel<%d> (tcgen05.mma kind::i8, weights expanded into tensor memory)"
+                                  % (16 if M <= 16 else 32)})
         del plans
         torch.cuda.empty_cache()
     return out
@@ -361,7 +363,7 @@ def run_ours(args):
                 "traffic_note": "algorithmic HBM bytes per launch (weights + scales + activations read once, output "
                                 "written once); the ncu capture of the M=2048 N=K=8192 case measured "
                                 "dram read = 1.004 x algorithmic (profiles/), this workload is too large to capture",
-                "kernel": "w2a8_umma_kernel<256,2,4,4,3,2> (tcgen05.mma kind::i8)", "ms_per_launch": round(ms_kernel, 4),
+                "kernel": "w2a8_umma_kernel<256,2,4,4,4,2> (tcgen05.mma kind::i8; token tile 256, one CTA per tile)", "ms_per_launch": round(ms_kernel, 4),
                 "peak_note": f"2 x {peaks['source']} bf16 burst TFLOP/s (no int8 figure is measured on this pool); "
                              f"vs 2 x sustained: {round(tops_kernel / (2 * peaks['bf16_tflops_sustained']), 4)}; "
                              f"vs nominal 4500: {round(tops_kernel / 4500.0, 4)}",

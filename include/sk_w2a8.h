@@ -106,6 +106,18 @@ int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,
                                 int32_t* partials, sk_stream_t stream);
 
+/* -------- weight preparation on the GPU ---------------------------------------------------------------
+ * Replaces, for a float32 weight, the host composition  quantize_to_uint2 (quantization.py:3-53)  then
+ * pack_matrix on the transposed codes (matrix_packer.py:3-36), bit for bit (same IEEE float32 operations: the
+ * 1e-9 floor, true division, round half to even, zero point 1).
+ *   w         float  [K, ld_w]   W[k, n], k = in-feature (groups of group_size rows along K), n = out-feature
+ *   w_packed  uint8  [N, K/4]    out, matrix_packer layout (what sk_w2a8_plan_create takes)
+ *   scale_f32 float  [K/G, N]    out or NULL: the scales as quantize_to_uint2 returns them
+ *   scale_f16 half   [K/G, N]    out or NULL: rounded to nearest even, what the GEMM consumes
+ * group_size % 4 == 0, K % group_size == 0, ld_w >= N.  Inputs must be finite. */
+int sk_w2a8_quantize_weight(const float* w, int64_t ld_w, int64_t K, int64_t N, int group_size, uint8_t* w_packed,
+                            float* scale_f32, void* scale_f16, sk_stream_t stream);
+
 /* -------- activation side of the Llama MLP block -----------------------------------------------------
  * The reference has no activation quantiser (its prototype is fed ready-made e4m3 tensors,
  * wgmma_sm90_W2A8.cu:541-552).  Definition used here, per token row:

@@ -13,6 +13,7 @@
 #include "activation.cuh"
 #include "w2a8_umma.cuh"
 #include "w2a8_decode.cuh"
+#include "weight_prep.cuh"
 
 namespace sk {
 
@@ -731,6 +732,22 @@ int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* sp
 }
 
 // ---------------------------------------------------------------------------------------------- activation side
+int sk_w2a8_quantize_weight(const float* w, int64_t ld_w, int64_t K, int64_t N, int group_size, uint8_t* w_packed,
+                            float* scale_f32, void* scale_f16, sk_stream_t stream) {
+  if (!w || !w_packed || (!scale_f32 && !scale_f16)) return SK_ERR_NULL_POINTER;
+  if (K <= 0 || N <= 0 || group_size <= 0 || (group_size % 4) != 0 || (K % group_size) != 0 || ld_w < N ||
+      K > (1LL << 30) || N > (1LL << 30) || K / group_size > 65535)
+    return SK_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(w) & 3) || (scale_f16 && (reinterpret_cast<uintptr_t>(scale_f16) & 1)) ||
+      (scale_f32 && (reinterpret_cast<uintptr_t>(scale_f32) & 3)))
+    return SK_ERR_BAD_ALIGNMENT;
+  const dim3 grid(static_cast<unsigned>((N + sk::kPrepThreads - 1) / sk::kPrepThreads), static_cast<unsigned>(K / group_size));
+  sk::quantize_pack_weight_kernel<<<grid, sk::kPrepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      w, ld_w, static_cast<int>(K), static_cast<int>(N), group_size, w_packed, scale_f32, static_cast<__half*>(scale_f16));
+  if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
+  return SK_OK;
+}
+
 int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int64_t K, int8_t* x_q, int64_t ld_q,
                                 float* x_scale, sk_stream_t stream) {
   if (!x_f16 || !x_q || !x_scale) return SK_ERR_NULL_POINTER;

@@ -105,6 +105,24 @@ at::Tensor partials(int64_t handle, const at::Tensor& x_q, int64_t N, int64_t K,
   return out;
 }
 
+// float32 W[K, N] -> (w_packed uint8 [N, K/4], w_scale float16 [K/G, N], scales float32 [K/G, N])
+std::tuple<at::Tensor, at::Tensor, at::Tensor> quantize_weight(const at::Tensor& w_kn, int64_t group_size) {
+  TORCH_CHECK(w_kn.is_cuda() && w_kn.scalar_type() == at::kFloat && w_kn.dim() == 2 && w_kn.stride(1) == 1,
+              "w must be a 2-D CUDA float32 tensor [K, N] with unit inner stride");
+  const int64_t K = w_kn.size(0), N = w_kn.size(1);
+  TORCH_CHECK(group_size > 0 && group_size % 4 == 0 && K % group_size == 0, "K must be a multiple of group_size (a multiple of 4)");
+  at::Tensor packed = at::empty({N, K / 4}, w_kn.options().dtype(at::kByte));
+  at::Tensor s16 = at::empty({K / group_size, N}, w_kn.options().dtype(at::kHalf));
+  at::Tensor s32 = at::empty({K / group_size, N}, w_kn.options().dtype(at::kFloat));
+  if (K == 0 || N == 0) return {packed, s16, s32};
+  c10::cuda::CUDAGuard guard(w_kn.device());
+  check(sk_w2a8_quantize_weight(w_kn.data_ptr<float>(), w_kn.stride(0), K, N, static_cast<int>(group_size),
+                                packed.data_ptr<uint8_t>(), s32.data_ptr<float>(), s16.data_ptr(),
+                                at::cuda::getCurrentCUDAStream().stream()),
+        "w2a8_quantize_weight");
+  return {packed, s16, s32};
+}
+
 std::tuple<at::Tensor, at::Tensor> quantize_activation(const at::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kHalf && x.dim() == 2 && x.stride(1) == 1,
               "x must be a 2-D CUDA float16 tensor with unit inner stride");
@@ -189,6 +207,7 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
   m.def("quantize_activation_int8(Tensor x) -> (Tensor, Tensor)", &quantize_activation);
+  m.def("w2a8_quantize_weight(Tensor w_kn, int group_size) -> (Tensor, Tensor, Tensor)", &quantize_weight);
   m.def("silu_mul_quantize_int8(Tensor gate_up) -> (Tensor, Tensor)", &silu_mul_quantize);
   m.def("w2a8_mlp_forward(int gate_up_plan, int down_plan, Tensor x, int hidden_out, bool bf16_out) -> Tensor", &mlp_forward);
   m.def("w2a8_repack(Tensor w_packed) -> Tensor", &repack);

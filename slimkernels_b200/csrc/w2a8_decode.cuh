@@ -5,17 +5,27 @@
 // of a CTA wait for one another.  Compared with the general kernel (w2a8_umma.cuh) this one
 //   * moves FOUR 128-wide K blocks per pipeline stage: one 16 KiB bulk copy of tiled weights (consecutive K blocks
 //     of a feature tile are contiguous in the tiled layout) plus four small activation boxes, so a CTA has up to
-//     64 KiB of weights in flight and the barriers are passed once per 512 K instead of once per 128;
-//   * expands the 2-bit codes straight into TENSOR MEMORY (tcgen05.st), two K blocks per hand-over, and feeds
-//     the MMA its weight operand from there (tcgen05.mma with the A operand in tensor memory): the expanded int8
-//     weights -- four times the packed bytes -- never touch shared memory;
-//   * keeps two sets of accumulator buffers (64 columns each): the MMAs of one set of scale groups run while the
-//     epilogue drains the other with a single wait and one pair of tensor-memory loads per set;
+//     64 KiB of weights in flight and the load barriers are passed once per 512 K instead of once per 128;
+//   * expands the 2-bit codes straight into TENSOR MEMORY (tcgen05.st), two K blocks ("half a stage") per
+//     hand-over, and feeds the MMA its weight operand from there (tcgen05.mma with the A operand in tensor memory,
+//     ~10 cycles per 128x16x32 MMA against ~40 with A in shared memory): the expanded int8 weights -- four times
+//     the packed bytes -- never touch shared memory;
+//   * issues ONE tcgen05.commit per half stage.  Its barrier tells the producer that a stage may be refilled, the
+//     expanders that a tensor-memory weight buffer may be overwritten and the epilogue that an accumulator set is
+//     complete (an mbarrier phase can be watched by any number of waiters); a commit stalls the issuing thread for
+//     hundreds of cycles, several times the MMAs of a decode-sized tile;
+//   * keeps two accumulator sets (one per half stage, two scale groups each): the MMAs of one half stage run while
+//     the epilogue drains the other with a single wait;
 //   * fits two CTAs on an SM (256 tensor-memory columns, < 113 KiB of shared memory, 384 threads each), which
-//     smooths out tile counts that are not a multiple of the SM count.
+//     smooths out tile counts that are not a multiple of the SM count;
+//   * is launched as a programmatic dependent launch: set-up and the weight copies of the first stages start
+//     while the previous kernel in the stream is still finishing; activations, token scales and outputs are
+//     touched only after griddepcontrol.wait.
 // The arithmetic is the one of the general kernel: accumulators pre-set once to the bias 2^22 and never reset,
-// running sums read as denormal floats, summation by parts over the 2 * kGroupsPerSet accumulator buffers, split-K
-// over a thread-block cluster with a fixed-order reduction through distributed shared memory.
+// running sums read as denormal floats, summation by parts over the four accumulator buffers.  Split-K runs over a
+// thread-block cluster: every CTA pushes its partial sums into the shared memory of the CTA that owns the token
+// row (remote stores, which do not stall the way remote loads do), one cluster barrier, then every CTA sums its
+// rows in rank order (deterministic, no global scratch).
 //
 // Like the general kernel this replaces the reference's gemm_device
 // (slimkernels/cute/gemm/wgmma_sm90_W2A8.cu:165-424); it shares no code with it.

@@ -94,6 +94,69 @@ def prepare_weight(weight_kn: np.ndarray, group_size: int = 128):
 
 
 # --------------------------------------------------------------------------------------------------
+# Serialised container of one quantised weight (the on-disk form of the operand pair).  The reference has
+# none (its helpers only return arrays); this one is little-endian and self-describing:
+#   bytes 0..7    magic  b"SKW2A8" + b"\x00" + version byte (1)
+#   5 x int64     N (out-features), K (in-features), group_size, zero_point, scale dtype code (2 = float16)
+#   N * K / 4     w_packed, matrix_packer layout (row n, byte j = codes k = 4j .. 4j+3, k = 4j in bits 7:6)
+#   K/G * N * 2   w_scale, float16 [K/G, N]
+#   uint32        CRC-32 of every byte before it
+# --------------------------------------------------------------------------------------------------
+_MAGIC = b"SKW2A8\x00\x01"
+
+
+def dumps_weight(w_packed: np.ndarray, w_scale: np.ndarray, group_size: int, zero_point: int = ZERO_POINT) -> bytes:
+    """Serialise (w_packed uint8 [N, K/4], w_scale float16 [K/G, N]) into the container described above."""
+    import struct
+    import zlib
+    if w_packed.dtype != np.uint8 or w_packed.ndim != 2:
+        raise TypeError("w_packed must be a 2-D uint8 array")
+    if w_scale.dtype != np.float16 or w_scale.ndim != 2:
+        raise TypeError("w_scale must be a 2-D float16 array")
+    N, K = w_packed.shape[0], w_packed.shape[1] * 4
+    if group_size <= 0 or K % group_size or w_scale.shape != (K // group_size, N):
+        raise ValueError(f"w_scale shape {w_scale.shape} does not match ({K // max(group_size, 1)}, {N})")
+    if not 0 <= zero_point <= 3:
+        raise ValueError("zero_point must be in 0..3")
+    body = (_MAGIC + struct.pack("<5q", N, K, group_size, zero_point, 2) +
+            np.ascontiguousarray(w_packed).tobytes() + np.ascontiguousarray(w_scale).astype("<f2").tobytes())
+    return body + struct.pack("<I", zlib.crc32(body) & 0xFFFFFFFF)
+
+
+def loads_weight(blob: bytes) -> dict:
+    """Inverse of ``dumps_weight``: {"w_packed", "w_scale", "group_size", "zero_point"}; ValueError if damaged."""
+    import struct
+    import zlib
+    head = len(_MAGIC) + 40
+    if len(blob) < head + 4 or blob[:len(_MAGIC) - 1] != _MAGIC[:-1]:
+        raise ValueError("not a W2A8 weight container")
+    if blob[len(_MAGIC) - 1] != _MAGIC[-1]:
+        raise ValueError(f"unsupported container version {blob[len(_MAGIC) - 1]}")
+    N, K, G, zp, sdt = struct.unpack("<5q", blob[len(_MAGIC):head])
+    if N <= 0 or K <= 0 or G <= 0 or K % 4 or K % G or not 0 <= zp <= 3 or sdt != 2:
+        raise ValueError("inconsistent container header")
+    n_packed, n_scale = N * K // 4, (K // G) * N * 2
+    if len(blob) != head + n_packed + n_scale + 4:
+        raise ValueError("container length does not match its header")
+    (crc,) = struct.unpack("<I", blob[-4:])
+    if crc != (zlib.crc32(blob[:-4]) & 0xFFFFFFFF):
+        raise ValueError("container checksum mismatch")
+    w_packed = np.frombuffer(blob, dtype=np.uint8, count=n_packed, offset=head).reshape(N, K // 4).copy()
+    w_scale = np.frombuffer(blob, dtype="<f2", count=n_scale // 2, offset=head + n_packed).reshape(K // G, N)
+    return {"w_packed": w_packed, "w_scale": w_scale.astype(np.float16), "group_size": int(G), "zero_point": int(zp)}
+
+
+def save_weight(path, w_packed, w_scale, group_size, zero_point=ZERO_POINT) -> None:
+    with open(path, "wb") as f:
+        f.write(dumps_weight(w_packed, w_scale, group_size, zero_point))
+
+
+def load_weight(path) -> dict:
+    with open(path, "rb") as f:
+        return loads_weight(f.read())
+
+
+# --------------------------------------------------------------------------------------------------
 # Tiled weight order consumed by the sm_100a kernel (a pure permutation of the 2-bit codes).
 # Block (tile T of 128 rows, k-block B of 128 codes) is 4096 bytes at (T * k_blocks + B) * 4096; the
 # little-endian 32-bit word of (row r, 16-code chunk c) sits at byte (c // 4) * 2048 + r * 16 + (c % 4) * 4

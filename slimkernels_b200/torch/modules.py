@@ -24,6 +24,15 @@ def silu_mul_quantize_int8(gate_up):
     return torch.ops.slimkernels.silu_mul_quantize_int8(gate_up)
 
 
+def prepare_weight_gpu(weight_kn, group_size=128):
+    """float32 W[K, N] (CUDA) -> (w_packed uint8 [N, K/4], w_scale float16 [K/G, N]) on the GPU: the same bits as
+    format.prepare_weight, i.e. the reference's quantize_to_uint2 (quantization.py:3) + pack_matrix
+    (matrix_packer.py:3) on the transposed codes."""
+    load_extension()
+    packed, s16, _ = torch.ops.slimkernels.w2a8_quantize_weight(weight_kn.contiguous(), group_size)
+    return packed, s16
+
+
 class W2A8Linear(nn.Module):
     """y = dequant(w_packed, w_scale) applied to dynamically int8-quantised activations.
 
@@ -40,10 +49,10 @@ class W2A8Linear(nn.Module):
 
     @classmethod
     def from_float(cls, weight_out_in, group_size=128, device="cuda", out_dtype=torch.float16):
-        """Quantise a float weight [out_features, in_features] with the reference's rule (host side)."""
-        from ..format import prepare_weight
-        w_packed, w_scale = prepare_weight(weight_out_in.detach().float().cpu().numpy().T.copy(), group_size)
-        return cls(torch.from_numpy(w_packed).to(device), torch.from_numpy(w_scale).to(device), group_size, 1, out_dtype)
+        """Quantise a float weight [out_features, in_features] with the reference's rule, on the GPU."""
+        w_kn = weight_out_in.detach().to(device=device, dtype=torch.float32).t().contiguous()
+        w_packed, w_scale = prepare_weight_gpu(w_kn, group_size)
+        return cls(w_packed, w_scale, group_size, 1, out_dtype)
 
     def plan(self) -> W2A8Plan:
         if self._plan is None:

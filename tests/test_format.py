@@ -124,3 +124,28 @@ def test_workload_generator_is_seeded_and_in_range():
     assert x_scale.dtype == np.float32 and 0.005 <= x_scale.min() and x_scale.max() <= 0.02
     assert w_packed.shape == (130, 64) and w_scale.shape == (2, 130) and w_scale.dtype == np.float16
     assert 0.001 <= float(w_scale.min()) and float(w_scale.max()) <= 0.01
+
+
+def test_weight_container_round_trip_and_damage(tmp_path):
+    rng = np.random.default_rng(11)
+    w = rng.standard_normal((256, 40)).astype(np.float32)           # K = 256, N = 40
+    w_packed, w_scale = F.prepare_weight(w, 64)
+    blob = F.dumps_weight(w_packed, w_scale, 64)
+    back = F.loads_weight(blob)
+    np.testing.assert_array_equal(back["w_packed"], w_packed)
+    np.testing.assert_array_equal(back["w_scale"].view(np.uint16), w_scale.view(np.uint16))
+    assert back["group_size"] == 64 and back["zero_point"] == 1
+    F.save_weight(tmp_path / "w.skw", w_packed, w_scale, 64, zero_point=2)
+    assert F.load_weight(tmp_path / "w.skw")["zero_point"] == 2
+    damaged = bytearray(blob)
+    damaged[60] ^= 0x10
+    with pytest.raises(ValueError, match="checksum"):
+        F.loads_weight(bytes(damaged))
+    with pytest.raises(ValueError, match="length"):
+        F.loads_weight(blob[:-5] + blob[-4:])
+    with pytest.raises(ValueError, match="not a W2A8"):
+        F.loads_weight(b"x" * 100)
+    with pytest.raises(ValueError):
+        F.dumps_weight(w_packed, w_scale, 128)                      # scales do not match the group size
+    with pytest.raises(TypeError):
+        F.dumps_weight(w_packed.astype(np.int8), w_scale, 64)
