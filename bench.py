@@ -249,6 +249,44 @@ def decode_sweep(dev, peaks):
     return out
 
 
+def side_kernels_sweep(dev, peaks):
+    """The HBM-bound kernels either side of the GEMM (Llama-3-70B MLP block shapes): weight preparation, per-token
+    int8 quantiser, fused SiLU*up re-quantiser.  GB/s over the bytes each must move, against the measured HBM peak;
+    buffers are larger than L2 or cycled so that every pass streams from HBM."""
+    import torch
+    from slimkernels_b200.torch import prepare_weight_gpu, quantize_activation_int8, silu_mul_quantize_int8
+    out = []
+    st = torch.cuda.current_stream(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+
+    def add(name, shape, fn, nbytes, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        ms = time_events(fn, iters, st)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out.append({"kernel": name, "shape": shape, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),
+                    "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "algorithmic_bytes": nbytes})
+
+    K, N, G = 8192, 28672, 128                                   # one Llama-3-70B gate (or up) projection
+    w = torch.randn(K, N, device=dev, dtype=torch.float32, generator=gen) * 0.02
+    add("quantize_pack_weight_kernel", f"W float32 [{K}, {N}] G={G}", lambda: prepare_weight_gpu(w, G),
+        4 * K * N + K * N // 4 + 6 * (K // G) * N, 5)
+    del w
+    M, H, I = 8192, 8192, 28672
+    x = torch.randn(M, H, device=dev, dtype=torch.float16, generator=gen)
+    add("quantize_activation_kernel", f"x float16 [{M}, {H}]", lambda: quantize_activation_int8(x), 3 * M * H + 4 * M, 10)
+    del x
+    M = 2048
+    gu = torch.randn(M, 2 * I, device=dev, dtype=torch.float16, generator=gen)
+    add("silu_mul_quantize_kernel", f"gate_up float16 [{M}, {2 * I}]", lambda: silu_mul_quantize_int8(gu),
+        4 * M * I + M * I + 4 * M, 10)
+    del gu
+    torch.cuda.empty_cache()
+    return out
+
+
 def prefill_sweep(dev, peaks):
     import torch
     from slimkernels_b200 import workloads as W
@@ -352,8 +390,10 @@ def run_ours(args):
     value = 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
 
     # ---- dominant kernel alone (this rank's GEMM launch), CUDA events on the launching stream
+    # (on one GPU the step IS that launch: the timed region above is the measurement; with several GPUs the step also
+    # holds the exchange, so the rank's GEMM is timed again on its own)
     barrier()
-    ms_kernel = max_over_ranks(time_events(lambda: op.local_gemm(d_x, d_xs), args.steps, stream))
+    ms_kernel = ms_step if world == 1 else max_over_ranks(time_events(lambda: op.local_gemm(d_x, d_xs), args.steps, stream))
     tops_kernel = 2.0 * M * n_local * K / (ms_kernel * 1e-3) / 1e12
     peak_int8 = 2.0 * peaks["bf16_tflops"]
     groups = K // G
@@ -401,6 +441,7 @@ def run_ours(args):
         pre, lib_tops = prefill_sweep(dev, peaks)
         line["prefill_sweep"] = pre
         line["library_int8_gemm_tops_8192"] = None if lib_tops is None else round(lib_tops, 1)
+        line["side_kernels"] = side_kernels_sweep(dev, peaks)
     if world == 1 and rank == 0:
         line["cpu_baseline"] = run_cpu_baseline()
     if rank == 0:
