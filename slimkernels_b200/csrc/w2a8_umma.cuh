@@ -149,23 +149,23 @@ struct KernelTraits {
   // sets of TMEM-load registers and take registers from the other warpgroup(s) with setmaxnreg.  The CTA's pool
   // is what it was given at launch (kLaunchRegs per thread); setmaxnreg.inc BLOCKS until the pool can serve it,
   // so the budgets must add up to no more than the pool or the kernel hangs:
-  //   BLOCK_M 256, 4 expander warps: 512 threads, 128 at launch -> epilogue 216, expanders 40, control 40
+  //   BLOCK_M 256, 4 expander warps: 512 threads, 128 at launch -> epilogue 224, expanders 32, control 32
   //   BLOCK_M 256, 2 expander warps: 384 threads, 168 at launch -> epilogue 224, expanders + control 56
   //   BLOCK_M 128:                   512 threads, 128 at launch -> epilogue 168, others 88
   static constexpr bool kUseSetMaxNReg = (EPI_WGS == 2);
   static constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
   static constexpr bool kBig = kColsPerWg > 96;
-  static constexpr int kEpiRegs = kBig ? (kThreads == 384 ? 224 : 216) : 168;
-  static constexpr int kExpRegs = kBig ? 40 : 88;                         // warpgroup holding the expander warps
-  static constexpr int kCtlRegs = kBig ? (kThreads == 384 ? 56 : 40) : 88;   // warpgroup holding producer + MMA warps
+  static constexpr int kEpiRegs = kBig ? 224 : 168;
+  static constexpr int kExpRegs = kBig ? 32 : 88;                         // warpgroup holding the expander warps
+  static constexpr int kCtlRegs = kBig ? (kThreads == 384 ? 56 : 32) : 88;   // warpgroup holding producer + MMA warps
   static constexpr int kExpWgThreads = (EXP_WARPS == 4) ? 128 : 0;        // expanders have a warpgroup of their own
   static_assert(!kUseSetMaxNReg ||
                     kEpiThreads * kEpiRegs + kExpWgThreads * kExpRegs +
                             (kThreads - kEpiThreads - kExpWgThreads) * kCtlRegs <= kThreads * kLaunchRegs,
                 "setmaxnreg budgets exceed the registers the CTA owns");
-  // Load chunk c+1 from TMEM while chunk c is consumed (where registers allow: two warps per scheduler
-  // already overlap each other's load latency).
-  static constexpr bool kDoubleBuf = (kNumChunks > 1) && (kColsPerWg <= 64);
+  // Load chunk c+1 from TMEM while chunk c is consumed (two sets of load registers; worth 1-3 % on the 256-token
+  // tile, where it needs the epilogue's 224-register budget).
+  static constexpr bool kDoubleBuf = (kNumChunks > 1);
   static constexpr int kMinBlocks = (BLOCK_M <= 32) ? 2 : 1;
   static_assert(kMinBlocks * kThreads <= 2048, "threads per SM");
 };
@@ -652,7 +652,9 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // TMEM loads are software-pipelined across chunks AND groups: while chunk c is consumed the load of the
     // next chunk -- or of the first chunk of the next group -- is already in flight.
     constexpr bool kPipelined = false;   // cross-group prefetch costs more registers than the epilogue has
-    constexpr int kBufMask = T::kDoubleBuf ? 1 : 0;
+    // (the debug variant keeps one set of load registers: it also holds the dump addresses)
+    constexpr bool kDB = T::kDoubleBuf && !DUMP;
+    constexpr int kBufMask = kDB ? 1 : 0;
     uint32_t v[kBufMask + 1][kChunk];
     if constexpr (kPipelined) {
       if (g_begin < g_end) {
@@ -677,17 +679,17 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (!epi_ok) break;
         if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 1);
         tcgen05_fence_after_sync();
-        if constexpr (T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf, v[0]);
+        if constexpr (kDB) tmem_ld_chunk<kChunk>(buf, v[0]);
       }
       int ab_next = ab + 1;
       uint32_t aph_next = aph;
       if (ab_next == ACC_BUFS) { ab_next = 0; aph_next ^= 1; }
 #pragma unroll
       for (int c = 0; c < kNumChunks; ++c) {
-        if constexpr (!T::kDoubleBuf) tmem_ld_chunk<kChunk>(buf + c * kChunk, v[0]);
+        if constexpr (!kDB) tmem_ld_chunk<kChunk>(buf + c * kChunk, v[0]);
         tmem_ld_wait();
         if (threadIdx.x == 0 && c < 4) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 2 + c);
-        if constexpr (T::kDoubleBuf) {
+        if constexpr (kDB) {
           if (c + 1 < kNumChunks) {
             tmem_ld_chunk<kChunk>(buf + (c + 1) * kChunk, v[(c + 1) & kBufMask]);
           } else if (kPipelined && g + 1 < g_end) {
