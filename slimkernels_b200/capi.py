@@ -24,7 +24,7 @@ SK_ERR_STATIC_SCRATCH_TOO_SMALL = -10
 
 SK_OUT_F16, SK_OUT_BF16 = 0, 1
 SK_WEIGHT_ROWMAJOR, SK_WEIGHT_TILED = 0, 1
-SK_OPT_KERNEL, SK_OPT_TOKEN_TILE, SK_OPT_SPLIT_K, SK_OPT_PERSISTENT, SK_OPT_DEPENDENT_LAUNCH = 1, 2, 3, 4, 5
+SK_OPT_KERNEL, SK_OPT_TOKEN_TILE, SK_OPT_SPLIT_K, SK_OPT_PERSISTENT, SK_OPT_DEPENDENT_LAUNCH, SK_OPT_TMA_STORE = 1, 2, 3, 4, 5, 6
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_CUDA_CORE, KERNEL_TCGEN05_DECODE = 0, 1, 2, 3
 
 _i64, _int, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p

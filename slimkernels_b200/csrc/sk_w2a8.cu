@@ -165,7 +165,7 @@ struct sk_w2a8_plan {
   const __half* w_scale = nullptr;      // borrowed
   int* status = nullptr;                // device, owned
   int last_cuda_error = 0;
-  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0, opt_pdl = 0;
+  int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0, opt_pdl = 0, opt_tma_store = 0;
   std::vector<sk::CachedMap> maps;      // small cache of activation tensor maps
   std::mutex mu;
 };
@@ -181,6 +181,8 @@ static int cuda_fail(sk_w2a8_plan* plan, cudaError_t e) {
 #ifdef SK_TRACE
 static long long* g_trace_buffer = nullptr;
 #endif
+
+constexpr size_t kMapCache = 40;   // cached tensor maps per plan (activations and up to 8 output destinations)
 
 struct LaunchChoice {
   int kernel;      // 1 tcgen05 (general), 2 CUDA-core checker, 3 tcgen05 (decode: token tiles 16 / 32, group size 128)
@@ -227,8 +229,9 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
 
 template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int ACC_BUFS, bool DUMP, bool A_TMEM = false,
           bool PERSIST = false>
-static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtensorMap& out_map, const GemmParams& prm,
-                       int m_tiles, int split_k, int persistent_ctas, cudaStream_t stream) {
+static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtensorMap& out_map,
+                       const ExtraOutMaps& extra_maps, const GemmParams& prm, int m_tiles, int split_k,
+                       int persistent_ctas, cudaStream_t stream) {
   using L = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>;
   auto kern = w2a8_umma_kernel<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, DUMP, A_TMEM, PERSIST>;
   static int configured_device_mask[64] = {0};
@@ -251,7 +254,7 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtenso
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, out_map, prm);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, out_map, extra_maps, prm);
   if (e != cudaSuccess) return cuda_fail(plan, e);
   return SK_OK;
 }
@@ -322,25 +325,26 @@ __global__ void diff_partials_kernel(int32_t* __restrict__ partials, int groups,
 
 template <bool DUMP>
 static int dispatch_umma(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const CUtensorMap& out_map,
-                         const GemmParams& prm, int m_tiles, int split_k, int persistent_ctas, cudaStream_t stream) {
+                         const ExtraOutMaps& extra_maps, const GemmParams& prm, int m_tiles, int split_k,
+                         int persistent_ctas, cudaStream_t stream) {
   switch (token_tile) {
     // <tokens, epilogue warpgroups, expander warps, load stages, expanded stages, accumulator buffers>
-    case 16: return launch_umma<16, 1, 8, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
-    case 32: return launch_umma<32, 1, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
-    case 64: return launch_umma<64, 1, 4, 6, 6, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 16: return launch_umma<16, 1, 8, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, extra_maps, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 32: return launch_umma<32, 1, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, extra_maps, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 64: return launch_umma<64, 1, 4, 6, 6, kAccBufsSmall, DUMP>(plan, map, out_map, extra_maps, prm, m_tiles, split_k, persistent_ctas, stream);
     case 128:
       if constexpr (!DUMP)
         if (persistent_ctas > 0)
-          return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, false, false, true>(plan, map, out_map, prm, m_tiles, 1, persistent_ctas, stream);
-      return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+          return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, false, false, true>(plan, map, out_map, extra_maps, prm, m_tiles, 1, persistent_ctas, stream);
+      return launch_umma<128, 2, 4, 4, 4, kAccBufsSmall, DUMP>(plan, map, out_map, extra_maps, prm, m_tiles, split_k, persistent_ctas, stream);
     // 192 tokens: the expanded weights live in tensor memory (2 x 192 accumulator columns + 4 x 32 weight columns;
     // no expanded-weight ring in shared memory, so the load ring is 7 stages deep)
-    case 192: return launch_umma<192, 2, 4, 7, 4, kAccBufs256, DUMP, true>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+    case 192: return launch_umma<192, 2, 4, 7, 4, kAccBufs256, DUMP, true>(plan, map, out_map, extra_maps, prm, m_tiles, split_k, persistent_ctas, stream);
     case 256:
       if constexpr (!DUMP)
         if (persistent_ctas > 0)
-          return launch_umma<256, 2, 4, 4, 2, kAccBufs256, false, false, true>(plan, map, out_map, prm, m_tiles, 1, persistent_ctas, stream);
-      return launch_umma<256, 2, 4, 4, 4, kAccBufs256, DUMP>(plan, map, out_map, prm, m_tiles, split_k, persistent_ctas, stream);
+          return launch_umma<256, 2, 4, 4, 2, kAccBufs256, false, false, true>(plan, map, out_map, extra_maps, prm, m_tiles, 1, persistent_ctas, stream);
+      return launch_umma<256, 2, 4, 4, 4, kAccBufs256, DUMP>(plan, map, out_map, extra_maps, prm, m_tiles, split_k, persistent_ctas, stream);
     default: return SK_ERR_BAD_ARGUMENT;
   }
 }
@@ -362,31 +366,32 @@ static int get_x_map(sk_w2a8_plan* plan, const int8_t* x_q, long long M, long lo
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { plan->last_cuda_error = static_cast<int>(r); return SK_ERR_CUDA; }
-  if (plan->maps.size() >= 16) plan->maps.erase(plan->maps.begin());
+  if (plan->maps.size() >= kMapCache) plan->maps.erase(plan->maps.begin());
   plan->maps.push_back(cm);
   *out = cm.map;
   return SK_OK;
 }
 
-// Tensor map of an output buffer for the TMA stores of the persistent kernel: 16-bit elements, [M][N] with row
-// pitch ld_out, boxes of 128 features x 64 tokens, no swizzle.
-static int get_out_map(sk_w2a8_plan* plan, const void* out, long long M, long long ld_out, CUtensorMap* res) {
+// Tensor map of an output buffer for TMA stores: 16-bit elements, [M][N] with row pitch ld_out, boxes of 128
+// features x box_rows tokens (the whole tile, or 64-token rounds of the persistent kernel), no swizzle.
+static int get_out_map(sk_w2a8_plan* plan, const void* out, long long M, long long ld_out, int box_rows,
+                       CUtensorMap* res) {
   std::lock_guard<std::mutex> lock(plan->mu);
   for (const auto& c : plan->maps)
-    if (c.ptr == out && c.M == M && c.ld == ld_out && c.block_m == -1) { *res = c.map; return SK_OK; }
+    if (c.ptr == out && c.M == M && c.ld == ld_out && c.block_m == -box_rows) { *res = c.map; return SK_OK; }
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return SK_ERR_CUDA;
   CachedMap cm;
-  cm.ptr = out; cm.M = M; cm.ld = ld_out; cm.block_m = -1;
+  cm.ptr = out; cm.M = M; cm.ld = ld_out; cm.block_m = -box_rows;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(plan->N), static_cast<cuuint64_t>(M)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_out) * 2};
-  const cuuint32_t box[2] = {128u, 64u};
+  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1u, 1u};
   CUresult r = enc(&cm.map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(out), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { plan->last_cuda_error = static_cast<int>(r); return SK_ERR_CUDA; }
-  if (plan->maps.size() >= 16) plan->maps.erase(plan->maps.begin());
+  if (plan->maps.size() >= kMapCache) plan->maps.erase(plan->maps.begin());
   plan->maps.push_back(cm);
   *res = cm.map;
   return SK_OK;
@@ -468,16 +473,29 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
           if (reinterpret_cast<uintptr_t>(extra_outs[i]) & 15) persist = false;
       }
       CUtensorMap out_map = map;   // placeholder where the kernel does not use it
+      ExtraOutMaps extra_maps;
+      for (int i = 0; i < 7; ++i) extra_maps.map[i] = map;
       if (persist) {
-        rc = get_out_map(plan, out, M, ld_out, &out_map);
+        rc = get_out_map(plan, out, M, ld_out, 64, &out_map);
         if (rc != SK_OK) persist = false, rc = SK_OK;
+      }
+      // One CTA per tile: the staged tile leaves through one TMA store per destination where the buffers allow it
+      // (16-byte aligned, pitch a multiple of 8 elements, N a multiple of 8).
+      prm.tma_out = 0;
+      if (!persist && !partials && ch.kernel == 1 && ch.split_k == 1 && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
+          (reinterpret_cast<uintptr_t>(out) & 15) == 0 && plan->opt_tma_store != 1) {
+        bool ok = get_out_map(plan, out, M, ld_out, ch.token_tile, &out_map) == SK_OK;
+        for (int i = 0; ok && i < n_extra; ++i)
+          ok = (reinterpret_cast<uintptr_t>(extra_outs[i]) & 15) == 0 &&
+               get_out_map(plan, extra_outs[i], M, ld_out, ch.token_tile, &extra_maps.map[i]) == SK_OK;
+        prm.tma_out = ok ? 1 : 0;
       }
       if (m_tiles > 65535) rc = SK_ERR_BAD_SHAPE;
       else if (partials) {
         if (ch.kernel == 3)
           rc = ch.token_tile == 16 ? launch_decode<16, true>(plan, map, prm, m_tiles, 1, stream)
                                    : launch_decode<32, true>(plan, map, prm, m_tiles, 1, stream);
-        else rc = dispatch_umma<true>(plan, ch.token_tile, map, out_map, prm, m_tiles, 1, 0, stream);
+        else rc = dispatch_umma<true>(plan, ch.token_tile, map, out_map, extra_maps, prm, m_tiles, 1, 0, stream);
         if (rc == SK_OK) {
           const long long mn = M * plan->N;
           const int blocks = static_cast<int>(mn / 256 + 1 < 148 * 8 ? mn / 256 + 1 : 148 * 8);
@@ -489,7 +507,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       else if (ch.kernel == 3)
         rc = ch.token_tile == 16 ? launch_decode<16, false>(plan, map, prm, m_tiles, ch.split_k, stream)
                                  : launch_decode<32, false>(plan, map, prm, m_tiles, ch.split_k, stream);
-      else rc = dispatch_umma<false>(plan, ch.token_tile, map, out_map, prm, m_tiles, ch.split_k, persist ? ch.ctas : 0, stream);
+      else rc = dispatch_umma<false>(plan, ch.token_tile, map, out_map, extra_maps, prm, m_tiles, ch.split_k, persist ? ch.ctas : 0, stream);
     }
   }
   if (cur != plan->device) (void)cudaSetDevice(cur);
@@ -591,7 +609,7 @@ int sk_w2a8_plan_create(sk_w2a8_plan** out, int device, int64_t N, int64_t K, in
   plan->n_tiles = static_cast<int>((N + 127) / 128);
   plan->sm_count = sms;
   plan->w_scale = static_cast<const __half*>(w_scale_f16);
-  plan->maps.reserve(17);   // the tensor-map cache never grows past 16 entries: no host reallocation on the call path
+  plan->maps.reserve(sk::kMapCache + 1);   // the tensor-map cache never grows past kMapCache entries: no host reallocation on the call path
 
   int cur = -1;
   cudaGetDevice(&cur);
@@ -668,6 +686,10 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
     case SK_OPT_DEPENDENT_LAUNCH:
       if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
       plan->opt_pdl = static_cast<int>(value);
+      return SK_OK;
+    case SK_OPT_TMA_STORE:
+      if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_tma_store = static_cast<int>(value);
       return SK_OK;
     case SK_OPT_PERSISTENT:
       if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;

@@ -72,6 +72,9 @@ enum : int {
 #define SK_TRACE_BASE 0
 #endif
 
+// Tensor maps of the further destinations of an output tile (peer GPUs' buffers): [M][N] 16-bit, box 128 x BLOCK_M.
+struct ExtraOutMaps { CUtensorMap map[7]; };
+
 struct GemmParams {
   const uint8_t* w_tiled;     // [n_tiles][k_blocks][4096]
   const __half* w_scale;      // [groups, N]
@@ -88,6 +91,7 @@ struct GemmParams {
   int groups;                 // K / G
   int zero_point;
   int out_bf16;
+  int tma_out;                // 1: the output tile leaves through TMA stores (tensor maps of every destination given)
   int n_tiles;                // ceil(N / 128)
   int num_tiles;              // n_tiles * token tiles
 #ifdef SK_TRACE
@@ -275,7 +279,7 @@ template <int BLOCK_M, int EPI_WGS, int EXP_WARPS, int LSTAGES, int ESTAGES, int
 __global__ void __launch_bounds__(KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>::kThreads,
                                   KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>::kMinBlocks)
 w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_out,
-                 const GemmParams p) {
+                 const __grid_constant__ ExtraOutMaps tmap_extra, const GemmParams p) {
   using T = KernelTraits<BLOCK_M, EPI_WGS, EXP_WARPS, LSTAGES, ESTAGES, ACC_BUFS, A_TMEM, PERSIST>;
   constexpr int kChunk = T::kChunk;
   constexpr int kNumChunks = T::kNumChunks;
@@ -812,9 +816,20 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         uint16_t* st = reinterpret_cast<uint16_t*>(smem);   // [BLOCK_M][128] in the output dtype
         if (p.out_bf16) stage_tokens<kCols, true>(acc, 0, xs_s + col0, st + col0 * kTileN + row);
         else stage_tokens<kCols, false>(acc, 0, xs_s + col0, st + col0 * kTileN + row);
+        if (p.tma_out) fence_proxy_async_smem();   // the staged tile is read by the TMA (async proxy)
         named_barrier_sync(1, T::kEpiThreads);
-        // destination 0 is this GPU's buffer; the others are peer-mapped buffers of the other ranks (plain
-        // stores over NVLink, so the all-gather of the output overlaps the GEMM tile by tile)
+        // destination 0 is this GPU's buffer; the others are peer-mapped buffers of the other ranks (stores over
+        // NVLink, so the all-gather of the output overlaps the GEMM tile by tile)
+        if (p.tma_out) {
+          // one TMA store per destination moves the whole staged tile (clipped at the edges of the output) while
+          // the CTA winds down; the thread only waits until the stores have READ shared memory
+          if (threadIdx.x == 0) {
+            tma_store_2d(&tmap_out, n0, m0, smem_base);
+            for (int d = 0; d < p.n_extra; ++d) tma_store_2d(&tmap_extra.map[d], n0, m0, smem_base);
+            bulk_commit_group();
+            bulk_wait_group_read0();
+          }
+        } else
         for (int d = 0; d <= p.n_extra; ++d) {
           uint16_t* outp = reinterpret_cast<uint16_t*>(d == 0 ? p.out : p.out_extra[d - 1]);
           const bool vec_ok = (n0 + kTileN <= p.N) && (p.ld_out % 8 == 0) &&

@@ -45,12 +45,13 @@ class DeviceProblem:
         assert self.plan.device_status() == 0
         return out
 
-    def force(self, kernel=0, token_tile=0, split_k=0, persistent=0, dependent_launch=0):
+    def force(self, kernel=0, token_tile=0, split_k=0, persistent=0, dependent_launch=0, tma_store=0):
         self.plan.set_option(capi.SK_OPT_KERNEL, kernel)
         self.plan.set_option(capi.SK_OPT_TOKEN_TILE, token_tile)
         self.plan.set_option(capi.SK_OPT_SPLIT_K, split_k)
         self.plan.set_option(capi.SK_OPT_PERSISTENT, persistent)
         self.plan.set_option(capi.SK_OPT_DEPENDENT_LAUNCH, dependent_launch)
+        self.plan.set_option(capi.SK_OPT_TMA_STORE, tma_store)
         return self
 
 

@@ -132,6 +132,19 @@ def test_ragged_shapes(M, N, K, G):
     _check(random_problem(M, N, K, G, seed=M + N + K), G=G)
 
 
+@pytest.mark.parametrize("token_tile,M,N", [(64, 50, 392), (128, 200, 1000), (256, 300, 264), (256, 700, 1280)])
+def test_tma_store_output_matches_thread_stores(token_tile, M, N):
+    """General kernel, one CTA per tile: the tile leaves through one TMA store (clipped at ragged edges) or through
+    the epilogue threads' vector stores; same bits either way, nothing written outside [M, N]."""
+    x_q, xs, wp, ws = random_problem(M, N, 512, 128, seed=M + N)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    y_threads = to_np(dp.force(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, tma_store=1).gemm(ld_out=N + 64))
+    y_tma = to_np(dp.force(kernel=capi.KERNEL_TCGEN05, token_tile=token_tile, tma_store=2).gemm(ld_out=N + 64))
+    assert np.isnan(y_tma[:, N:]).all()
+    np.testing.assert_array_equal(y_tma[:, :N], y_threads[:, :N])
+    assert np.abs(y_tma[:, :N] - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+
+
 def test_checker_kernel_matches_oracle():
     prob = random_problem(19, 200, 512, 128, seed=5)
     _check(prob, force=dict(kernel=capi.KERNEL_CUDA_CORE))
