@@ -172,6 +172,7 @@ struct KernelTraits {
   static constexpr bool kDoubleBuf = (kNumChunks > 1);
   static constexpr int kMinBlocks = (BLOCK_M <= 32) ? 2 : 1;
   static_assert(kMinBlocks * kThreads <= 2048, "threads per SM");
+  static_assert(kEpiWarps + EXP_WARPS + 3 <= kWarps, "room for the producer warp and two MMA-issuing warps");
 };
 
 struct WaitCtx {
@@ -408,8 +409,14 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
       }
       __syncwarp();
-    } else if (warp == kMmaWarp) {
-      // ============================================================ MMA issuer (whole warp loops, one lane issues)
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+      // ============================================================ MMA issuers (whole warp loops, one lane issues)
+      // TWO warps take the scale groups in turn.  Between the MMAs of one group and those of the next a single
+      // issuing thread spends ~800 cycles on its commits, loop and barrier polls -- longer than the tensor core
+      // needs for what is queued -- so with one issuer the tensor pipe idles about half the time; with two, one
+      // warp's overhead overlaps the other's issue.  Consecutive groups use different accumulator buffers and
+      // different stages, and tcgen05.commit tracks the issuing thread's own MMAs, so the two streams are independent.
+      const int mma_id = warp - kMmaWarp;
       constexpr uint32_t idesc = make_idesc_i8(kTileN, BLOCK_M, /*a_signed=*/true, /*b_signed=*/true);
       const uint64_t a_desc0 = make_kmajor_sw128_desc(smem_base + T::kOffWx);
       const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_base + T::kOffX);
@@ -418,11 +425,28 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       bool ok = true;
       if (p.steps_per_group == 4) {
         // one K block == one scale group: four MMAs and three commits per iteration, nothing else
+        int turn = 0;                             // whose group this is (alternates over all K blocks of all tiles)
         for (int tile = tile_first; tile < tile_end && ok; tile += tile_step)
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, turn ^= 1) {
+          if (turn != mma_id) {                   // the other warp's group: only keep the ring state in step
+            if (++l == LSTAGES) { l = 0; lph ^= 1; }
+            if (++e == ESTAGES) { e = 0; eph ^= 1; }
+            if (++ab == ACC_BUFS) { ab = 0; aph ^= 1; }
+            continue;
+          }
+#ifdef SK_TRACE_MMA_FINE
+          if (lane == 0 && kb - kb_begin >= 8 && kb - kb_begin < 16) SK_TRACE_EVENT(5, (kb - kb_begin - 8) * 8 + 0);
+          ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull);
+          if (lane == 0 && kb - kb_begin >= 8 && kb - kb_begin < 16) SK_TRACE_EVENT(5, (kb - kb_begin - 8) * 8 + 1);
+          ok = ok && wait_bounded(bar_ex_full + 8 * e, eph, ctx, kStMmaExFull);
+          if (lane == 0 && kb - kb_begin >= 8 && kb - kb_begin < 16) SK_TRACE_EVENT(5, (kb - kb_begin - 8) * 8 + 2);
+          ok = ok && wait_bounded(bar_acc_empty + 8 * ab, aph, ctx, kStMmaAccEmpty);
+          if (lane == 0 && kb - kb_begin >= 8 && kb - kb_begin < 16) SK_TRACE_EVENT(5, (kb - kb_begin - 8) * 8 + 3);
+#else
           ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull) &&
                wait_bounded(bar_ex_full + 8 * e, eph, ctx, kStMmaExFull) &&
                wait_bounded(bar_acc_empty + 8 * ab, aph, ctx, kStMmaAccEmpty);
+#endif
           if (!ok) break;
           tcgen05_fence_after_sync();
           if (elect_one()) {
@@ -442,9 +466,15 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
               umma_i8(d, a_desc + 4, b_desc + 4, idesc, 1u);
               umma_i8(d, a_desc + 6, b_desc + 6, idesc, 1u);
             }
+#ifdef SK_TRACE_MMA_FINE
+            if (kb - kb_begin >= 8 && kb - kb_begin < 16) SK_TRACE_EVENT(5, (kb - kb_begin - 8) * 8 + 4);
+#endif
             umma_commit(bar_acc_full + 8 * ab);
             umma_commit(bar_ld_empty + 8 * l);
             if constexpr (!T::kTied) umma_commit(bar_ex_empty + 8 * e);
+#ifdef SK_TRACE_MMA_FINE
+            if (kb - kb_begin >= 8 && kb - kb_begin < 16) SK_TRACE_EVENT(5, (kb - kb_begin - 8) * 8 + 5);
+#endif
             SK_TRACE_EVENT(2, SK_TRACE_BASE + kb - kb_begin);
           }
           __syncwarp();
@@ -459,8 +489,9 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           if (++ab == ACC_BUFS) { ab = 0; aph ^= 1; }
         }
       } else {
-        // general group sizes (32, 64, 256, ...): track the position inside the group per 32-wide K step
+        // general group sizes (32, 64, 256, ...): one issuer, tracking the position inside the group per 32-wide K step
         int pos = 0;
+        if (mma_id == 0)
         for (int tile = tile_first; tile < tile_end && ok; tile += tile_step)
         for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
           ok = wait_bounded(bar_ld_full + 8 * l, lph, ctx, kStMmaLdFull) &&
@@ -653,20 +684,12 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     for (int i = 0; i <= ACC_BUFS; ++i) sr[i] = load_scale();
     float s_sum = 0.f;   // sum of the coefficients since the last bias flush
     int flush = 0;
-    // TMEM loads are software-pipelined across chunks AND groups: while chunk c is consumed the load of the
-    // next chunk -- or of the first chunk of the next group -- is already in flight.
-    constexpr bool kPipelined = false;   // cross-group prefetch costs more registers than the epilogue has
+    // TMEM loads are software-pipelined across the chunks of a group: while chunk c is consumed the load of chunk
+    // c + 1 is in flight (prefetching across groups as well costs more registers than the epilogue has).
     // (the debug variant keeps one set of load registers: it also holds the dump addresses)
     constexpr bool kDB = T::kDoubleBuf && !DUMP;
     constexpr int kBufMask = kDB ? 1 : 0;
     uint32_t v[kBufMask + 1][kChunk];
-    if constexpr (kPipelined) {
-      if (g_begin < g_end) {
-        epi_ok = wait_bounded(bar_acc_full, 0, ctx, kStEpilogueAccFull);
-        tcgen05_fence_after_sync();
-        tmem_ld_chunk<kChunk>(lane_addr, v[0]);
-      }
-    }
 #pragma unroll 1
     for (int g = g_begin; g < g_end && epi_ok; ++g) {
       // coefficient of this group's running sum
@@ -677,14 +700,12 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       const uint32_t buf = lane_addr + ab * BLOCK_M;
       // the last groups of a tile keep their buffers until these are back at the bias for the next tile (below)
       const bool keep_buf = more_tiles && g >= g_end - ACC_BUFS;
-      if constexpr (!kPipelined) {
-        if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 0);
-        epi_ok = wait_bounded(bar_acc_full + 8 * ab, aph, ctx, kStEpilogueAccFull);
-        if (!epi_ok) break;
-        if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 1);
-        tcgen05_fence_after_sync();
-        if constexpr (kDB) tmem_ld_chunk<kChunk>(buf, v[0]);
-      }
+      if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 0);
+      epi_ok = wait_bounded(bar_acc_full + 8 * ab, aph, ctx, kStEpilogueAccFull);
+      if (!epi_ok) break;
+      if (threadIdx.x == 0) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 1);
+      tcgen05_fence_after_sync();
+      if constexpr (kDB) tmem_ld_chunk<kChunk>(buf, v[0]);
       int ab_next = ab + 1;
       uint32_t aph_next = aph;
       if (ab_next == ACC_BUFS) { ab_next = 0; aph_next ^= 1; }
@@ -694,13 +715,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         tmem_ld_wait();
         if (threadIdx.x == 0 && c < 4) SK_TRACE_EVENT(7, (g - g_begin) * 8 + 2 + c);
         if constexpr (kDB) {
-          if (c + 1 < kNumChunks) {
-            tmem_ld_chunk<kChunk>(buf + (c + 1) * kChunk, v[(c + 1) & kBufMask]);
-          } else if (kPipelined && g + 1 < g_end) {
-            epi_ok = wait_bounded(bar_acc_full + 8 * ab_next, aph_next, ctx, kStEpilogueAccFull);
-            tcgen05_fence_after_sync();
-            tmem_ld_chunk<kChunk>(lane_addr + ab_next * BLOCK_M, v[0]);   // harmless if the wait gave up
-          }
+          if (c + 1 < kNumChunks) tmem_ld_chunk<kChunk>(buf + (c + 1) * kChunk, v[(c + 1) & kBufMask]);
         }
         if (c == kNumChunks - 1 && !keep_buf) {   // buffer fully read: hand it back to the MMA issuer (it keeps accumulating)
           tcgen05_fence_before_sync();
