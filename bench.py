@@ -401,9 +401,9 @@ def run_ours(args):
     roofline = {"bound": "tensor", "achieved": round(tops_kernel, 2), "peak": round(peak_int8, 1), "unit": "TOP/s",
                 "frac": round(tops_kernel / peak_int8, 4), "traffic": traffic,
                 "traffic_note": "algorithmic HBM bytes per launch (weights + scales + activations read once, output "
-                                "written once); the ncu capture of the M=2048 N=K=8192 case measured "
-                                "dram read = 1.004 x algorithmic (profiles/), this workload is too large to capture",
-                "kernel": "w2a8_umma_kernel<256,2,4,4,4,2> (tcgen05.mma kind::i8; token tile 256, one CTA per tile)", "ms_per_launch": round(ms_kernel, 4),
+                                "written once); the ncu capture of the M=4096 N=K=8192 case measured "
+                                "dram read = 1.06 x algorithmic (profiles/), this workload is too large to capture",
+                "kernel": "w2a8_umma_kernel<256,2,4,4,4,2> (tcgen05.mma kind::i8; token tile 256, one CTA per tile, two MMA-issuing warps)", "ms_per_launch": round(ms_kernel, 4),
                 "peak_note": f"2 x {peaks['source']} bf16 burst TFLOP/s (no int8 figure is measured on this pool); "
                              f"vs 2 x sustained: {round(tops_kernel / (2 * peaks['bf16_tflops_sustained']), 4)}; "
                              f"vs nominal 4500: {round(tops_kernel / 4500.0, 4)}",
