@@ -62,7 +62,7 @@ struct DecodeTraits {
   static constexpr int kTotal = kOffMisc + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;        // slack for 1024-byte alignment of the base
   static constexpr int kEpiWarps = 4, kExpWarps = 4;
-  static constexpr int kThreads = 384;                       // 4 epilogue + 4 expander + producer + MMA warps, + 2 idle
+  static constexpr int kThreads = 384;                       // 4 epilogue + 4 expander + producer + 2 MMA warps, + 1 idle
   static_assert(2 * kDynamicBytes <= 227 * 1024, "two CTAs per SM");
 };
 
@@ -165,12 +165,13 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       wsrc += static_cast<size_t>(min(T::kKbPerStage, nkb - i)) * kWpBytes;
       ++issued;
     }
-    // later rounds: a stage is refilled once the MMAs of its second half (of its previous use) are complete
+    // later rounds: a stage is refilled once the MMAs of both its halves (of its previous use) are complete
     for (int i = issued * T::kKbPerStage; i < nkb; i += T::kKbPerStage) {
       const int n = min(T::kKbPerStage, nkb - i);
-      {
-        const int u = 2 * (issued - S) + 1;
-        ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStProducerEmpty);
+      {   // both half stages of the stage's previous use (they are committed by different warps, in any order)
+        const int u = 2 * (issued - S);
+        ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStProducerEmpty) &&
+             wait_bounded(bar_sub_done + 8 * ((u + 1) % T::kSubRing), ((u + 1) / T::kSubRing) & 1, ctx, kStProducerEmpty);
         if (!ok) break;
       }
       if (elect_one()) {
@@ -199,19 +200,25 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarp) {
-    // ============================================================ MMA issuer (whole warp loops, one lane issues)
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+    // ============================================================ MMA issuers (whole warp loops, one lane issues)
+    // Two warps take the half stages in turn: between two half stages one issuing thread spends several hundred
+    // cycles on its commit, barrier polls and loop -- more than the MMAs of a decode-sized half stage take -- and
+    // consecutive half stages use different accumulator sets and different weight buffers, so the two streams are
+    // independent (tcgen05.commit tracks the issuing thread's own MMAs).
     constexpr uint32_t idesc = make_idesc_i8(kTileN, TOK, /*a_signed=*/true, /*b_signed=*/true);
     const uint64_t b_desc0 = make_kmajor_sw128_desc(smem_base + T::kStageWBytes);
-    int stage = 0, a = 0;                       // load stage; tensor-memory buffer of expanded weights
-    uint32_t lph = 0, eph = 0;
+    const int mma_id = warp - kMmaWarp;
     bool ok = true;
     const int num_subs = (nkb + 1) >> 1;
-    for (int u = 0; u < num_subs; ++u) {        // one half stage (two K blocks, eight MMAs, one accumulator set)
+    for (int u = mma_id; u < num_subs; u += 2) {   // one half stage: two K blocks, eight MMAs, one accumulator set
       const int i0 = 2 * u;
-      if ((u & 1) == 0) ok = wait_bounded(bar_ld_full + 8 * stage, lph, ctx, kStMmaLdFull);
-      if (ok) ok = wait_bounded(bar_ex_full + 8 * a, eph, ctx, kStMmaExFull);
-      if (ok) ok = wait_bounded(bar_acc_empty + 8 * (u & 1), (u >> 1) & 1, ctx, kStMmaAccEmpty);
+      const int q = u >> 1;                     // load stage counter
+      const int stage = q % S;
+      const int a = u % T::kASubs;              // tensor-memory buffer of expanded weights
+      ok = wait_bounded(bar_ld_full + 8 * stage, (q / S) & 1, ctx, kStMmaLdFull) &&
+           wait_bounded(bar_ex_full + 8 * a, (u / T::kASubs) & 1, ctx, kStMmaExFull) &&
+           wait_bounded(bar_acc_empty + 8 * (u & 1), (u >> 1) & 1, ctx, kStMmaAccEmpty);
       if (!ok) break;
       tcgen05_fence_after_sync();
       if (elect_one()) {
@@ -231,8 +238,6 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
         SK_TRACE_EVENT(2, u);
       }
       __syncwarp();
-      if ((u & 1) && ++stage == S) { stage = 0; lph ^= 1; }
-      if (++a == T::kASubs) { a = 0; eph ^= 1; }
     }
     __syncwarp();
   } else if (warp >= kExpWarp0 && warp < kProducerWarp) {
