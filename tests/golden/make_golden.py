@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checked out (it is not needed at test time):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 It imports matrix_packer.py and quantization.py from the reference tree, feeds them
 seeded inputs and stores inputs + outputs.  The composed GEMM vectors follow the
@@ -78,4 +78,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
