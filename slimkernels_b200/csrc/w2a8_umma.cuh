@@ -6,13 +6,15 @@
 //      memory stages guarded by mbarriers;
 //   2. expander warps turn the 2-bit codes into int8 bytes (code - zero_point) with a byte-permute look-up
 //      (prmt), written straight into the 128-byte-swizzled K-major layout the tensor core reads;
-//   3. an MMA warp issues tcgen05.mma kind::i8 (128 x BLOCK_M x 32 per instruction): the weights are the
-//      "A"/M operand, the tokens the "B"/N operand, int32 accumulators live in tensor memory, one accumulator
-//      buffer per scale group (ACC_BUFS buffers, so later groups accumulate while earlier ones drain);
+//   3. two MMA warps, taking the scale groups in turn, issue tcgen05.mma kind::i8 (128 x BLOCK_M x 32 per
+//      instruction): the weights are the "A"/M operand, the tokens the "B"/N operand, int32 accumulators live in
+//      tensor memory, one accumulator buffer per scale group (ACC_BUFS buffers, so later groups accumulate while
+//      earlier ones drain);
 //   4. one or two epilogue warpgroups read each finished group from tensor memory (lane = output feature,
 //      column = token), multiply by that feature's group scale (a per-thread scalar) and accumulate in fp32;
 //      at the end the per-token activation scale is applied, the tile is transposed through shared memory
-//      and written with 16-byte coalesced stores.
+//      and leaves through one TMA store per destination (16-byte coalesced stores by the threads where the
+//      output's alignment rules that out).
 //
 // Integer -> float without a conversion instruction, and without ever resetting an accumulator:
 //   * every accumulator buffer is pre-set ONCE per tile to the bias B = 2^22 and the MMAs always accumulate, so
@@ -26,8 +28,9 @@
 // epilogue has to spare.  The debug entry point stores the running sums; the host differences them into P.
 //
 // The producer and MMA warps run their loops warp-uniformly (all lanes wait, one elected lane issues) and keep
-// the loop bodies short: a single warp retires dependent instructions several cycles apart, and the loop must
-// turn around in less than the tensor-core time of one K block.  mbarriers count one arrival per warp.
+// the loop bodies short: a single warp retires dependent instructions several cycles apart.  Even so one issuing
+// thread needs longer for its commits, barrier polls and loop between two groups than the tensor core needs for a
+// group, hence the two issuers.  mbarriers count one arrival per warp.
 //
 // With SPLIT_K > 1 the CTAs of one thread-block cluster split the groups of a tile and reduce their fp32
 // accumulators through distributed shared memory in a fixed order (deterministic, no global scratch).

@@ -60,6 +60,46 @@ class W2A8Plan:
         torch.ops.slimkernels.w2a8_plan_gemm_out(self._h, x_q, x_scale, out, self.K)
         return out
 
+    def gemm_host(self, h_x_q, h_x_scale, h_out, chunk_tokens: int = 512):
+        """The GEMM for operands that live in (pinned) HOST memory: int8 [M, K] and float32 [M] in, [M, N] out.
+
+        The tokens are cut into chunks; the host->device copy of chunk i+1, the GEMM of chunk i and the
+        device->host copy of chunk i-1 run on three streams at once, so a call costs about as much as its largest leg
+        (for a wide layer that is the copy of the output over PCIe) instead of the sum of the three.  Device staging
+        buffers are allocated on first use and kept.  Returns h_out; the caller's stream waits for everything.
+        """
+        dev = self._w.device
+        M = h_x_q.shape[0]
+        if h_x_q.device.type != "cpu" or h_out.device.type != "cpu" or h_x_scale.device.type != "cpu":
+            raise TypeError("gemm_host takes host tensors")
+        if tuple(h_out.shape) != (M, self.N) or h_out.dtype != self.out_dtype or h_x_q.shape[1] != self.K:
+            raise ValueError("shape / dtype mismatch")
+        st = getattr(self, "_host_state", None)
+        if st is None or st["M"] < M:
+            st = {"M": M, "x": torch.empty(M, self.K, dtype=torch.int8, device=dev),
+                  "xs": torch.empty(M, dtype=torch.float32, device=dev),
+                  "out": torch.empty(M, self.N, dtype=self.out_dtype, device=dev),
+                  "s_in": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev)}
+            self._host_state = st
+        cur = torch.cuda.current_stream(dev)
+        s_in, s_out = st["s_in"], st["s_out"]
+        s_in.wait_stream(cur)                     # earlier users of the staging buffers are done
+        s_out.wait_stream(cur)
+        for lo in range(0, M, chunk_tokens):
+            hi = min(M, lo + chunk_tokens)
+            with torch.cuda.stream(s_in):
+                st["x"][lo:hi].copy_(h_x_q[lo:hi], non_blocking=True)
+                st["xs"][lo:hi].copy_(h_x_scale[lo:hi], non_blocking=True)
+                ev_in = s_in.record_event()
+            cur.wait_event(ev_in)
+            self.gemm(st["x"][lo:hi], st["xs"][lo:hi], out=st["out"][lo:hi])
+            ev_c = cur.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c)
+                h_out[lo:hi].copy_(st["out"][lo:hi], non_blocking=True)
+        cur.wait_stream(s_out)
+        return h_out
+
     def gemm_scatter(self, x_q, x_scale, out_ptrs, ld_out: int, col_offset: int) -> None:
         """Writes the [M, N] result at column `col_offset` of every [M, ld_out] buffer in `out_ptrs` (raw device
         pointers: this GPU's buffer first, then peer-mapped buffers of the other ranks)."""
