@@ -284,9 +284,13 @@ static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmP
     attr[na].val.clusterDim.z = split_k;
     ++na;
   }
-  if (!DUMP && plan->opt_pdl != 1) {
-    // programmatic dependent launch: this kernel's set-up may overlap the tail of the previous kernel in the stream
-    // (the kernel itself waits for that kernel before it touches activations or outputs)
+  // Programmatic dependent launch: this kernel's set-up and first weight copies may overlap the tail of the previous
+  // kernel in the stream (the kernel itself waits for that kernel before it touches activations or outputs).
+  // Measured: it pays when the grid does not fit one CTA per SM (the early CTAs fill SMs the previous kernel's last
+  // wave leaves idle: -8..-17 %), and costs when it does (the early CTAs only poll next to the running ones:
+  // +8..+25 %), so by default it is used for the former only.
+  const long long ctas = static_cast<long long>(plan->n_tiles) * m_tiles * split_k;
+  if (!DUMP && (plan->opt_pdl == 2 || (plan->opt_pdl == 0 && ctas > plan->sm_count))) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
