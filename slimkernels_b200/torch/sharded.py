@@ -1,4 +1,8 @@
-"""N-sharded execution of one W2A8 GEMM across the GPUs of a node (one process per GPU).
+"""Sharded execution of one W2A8 GEMM across the GPUs of a node (one process per GPU): N-sharded with an all-gather
+(ShardedW2A8Gemm) and K-sharded with a reduce-scatter (KShardedW2A8Gemm, for a projection whose input is already
+split by features, like the down projection behind an N-sharded gate+up).
+
+N-sharding:
 
 Output features are independent, so rank r owns rows [r*N/R, (r+1)*N/R) of w_packed and the matching
 columns of w_scale; activations are replicated; K is not split, so no reduction is needed.  The only
@@ -94,6 +98,59 @@ class ShardedW2A8Gemm:
         dist.all_gather_into_tensor(gathered.view(self.world * M, self.N_local), local, group=self.group)
         # [R, M, N/R] -> [M, R, N/R] == [M, N]
         full.view(M, self.world, self.N_local).copy_(gathered.permute(1, 0, 2))
+        return full
+
+    __call__ = forward
+
+
+def shard_weight_k(w_packed, w_scale, world: int, rank: int, group_size: int = 128):
+    """This rank's K slice of (w_packed [N, K/4], w_scale [K/G, N]): in-features [r K/R, (r+1) K/R), whole groups."""
+    K = w_packed.shape[1] * 4
+    if K % (world * group_size) != 0:
+        raise ValueError(f"K={K} must be a multiple of world_size*group_size={world * group_size}")
+    per = K // world
+    return (w_packed[:, rank * per // 4:(rank + 1) * per // 4].contiguous(),
+            w_scale[rank * per // group_size:(rank + 1) * per // group_size].contiguous())
+
+
+class KShardedW2A8Gemm:
+    """K-sharded W2A8 GEMM: rank r holds the weight columns (in-features) [r K/R, (r+1) K/R) and receives the matching
+    slice of the activations, quantised per token ON ITS OWN slice (x_q_local int8 [M, K/R], x_scale_local fp32 [M]).
+
+    Every rank computes a partial [M, N]; the partials are reduce-scattered by token rows: rank r ends up with rows
+    [r M/R, (r+1) M/R) of the sum (``forward``), or ``forward_full`` all-gathers them back to [M, N].  The exchange
+    moves the partials in the output dtype and sums them in fp32 in rank order (deterministic), rounding once.
+    M must be a multiple of the world size.
+    """
+
+    def __init__(self, w_packed_local, w_scale_local, group=None, group_size=128, zero_point=1,
+                 out_dtype=torch.float16, plan_factory=W2A8Plan):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.N = w_packed_local.shape[0]
+        self.out_dtype = out_dtype
+        self.plan = plan_factory(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
+                                 out_dtype=out_dtype)
+
+    def forward(self, x_q_local, x_scale_local):
+        M = x_q_local.shape[0]
+        partial = self.plan.gemm(x_q_local, x_scale_local)                   # [M, N], this rank's share of the sum
+        if self.world == 1:
+            return partial
+        if M % self.world != 0:
+            raise ValueError(f"M={M} must be a multiple of the world size {self.world}")
+        rows = M // self.world
+        recv = torch.empty_like(partial)                                     # [R, M/R, N]: block j from rank j
+        dist.all_to_all_single(recv, partial.contiguous(), group=self.group)
+        return recv.view(self.world, rows, self.N).float().sum(dim=0).to(self.out_dtype)
+
+    def forward_full(self, x_q_local, x_scale_local):
+        mine = self.forward(x_q_local, x_scale_local)
+        if self.world == 1:
+            return mine
+        full = torch.empty(self.world * mine.shape[0], self.N, dtype=self.out_dtype, device=mine.device)
+        dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
         return full
 
     __call__ = forward

@@ -22,6 +22,8 @@ class OraclePlan:
     def gemm(self, x_q, x_scale, out=None):
         from oracle import w2a8_oracle as O
         y = torch.from_numpy(O.w2a8_gemm_int_path(x_q.numpy(), x_scale.numpy(), self.w_packed, self.w_scale, self.G, self.zp))
+        if out is None:
+            return y.to(self.dt)
         out.copy_(y.to(self.dt))
         return out
 
@@ -71,6 +73,54 @@ def test_two_rank_shard_and_gather_on_cpu():
     assert sorted(r[0] for r in results) == [0, 1]
     for _, equal, shape in results:
         assert equal and shape == (6, 512)
+
+
+def _worker_k(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import w2a8_oracle as O
+        from slimkernels_b200 import workloads as W
+        from slimkernels_b200.torch.sharded import KShardedW2A8Gemm, shard_weight_k
+        M, N, K, G = 8, 256, 512, 128
+        x_q, _, w_packed, w_scale = W.make_problem(M, N, K, G, seed=1)
+        rng = np.random.default_rng(7)
+        scales = rng.uniform(0.005, 0.02, size=(world, M)).astype(np.float32)      # every rank quantised its own slice
+        per = K // world
+        wl, sl = shard_weight_k(torch.from_numpy(w_packed), torch.from_numpy(w_scale), world, rank, G)
+        assert wl.shape == (N, per // 4) and sl.shape == (per // G, N) and wl.is_contiguous() and sl.is_contiguous()
+        op = KShardedW2A8Gemm(wl, sl, group_size=G, plan_factory=OraclePlan)
+        xl = torch.from_numpy(np.ascontiguousarray(x_q[:, rank * per:(rank + 1) * per]))
+        mine = op(xl, torch.from_numpy(scales[rank]))
+        full = op.forward_full(xl, torch.from_numpy(scales[rank]))
+        ref = sum(O.w2a8_gemm_int_path(np.ascontiguousarray(x_q[:, r * per:(r + 1) * per]), scales[r],
+                                       np.ascontiguousarray(w_packed[:, r * per // 4:(r + 1) * per // 4]),
+                                       w_scale[r * per // G:(r + 1) * per // G], G) for r in range(world))
+        rows = M // world
+        err_mine = float(np.abs(mine.float().numpy() - ref[rank * rows:(rank + 1) * rows]).max())
+        err_full = float(np.abs(full.float().numpy() - ref).max())
+        q.put((rank, err_mine, err_full, tuple(mine.shape), tuple(full.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_k_sharded_reduce_scatter_on_cpu():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_k, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=60) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in results) == [0, 1]
+    for _, err_mine, err_full, shape_mine, shape_full in results:
+        assert shape_mine == (4, 256) and shape_full == (8, 256)
+        assert err_mine <= 1e-2 and err_full <= 1e-2      # partials travel in fp16, the sum runs in fp32
 
 
 def test_shard_bounds_rejects_ragged_split():

@@ -1,4 +1,4 @@
-"""N-sharded W2A8 GEMM + NCCL all-gather on 2 GPUs (skipped where fewer are visible)."""
+"""N-sharded W2A8 GEMM + all-gather and K-sharded GEMM + reduce-scatter on 2 GPUs (skipped where fewer are visible)."""
 import os
 import socket
 import sys
@@ -61,3 +61,54 @@ def test_two_gpu_shard_and_allgather(built_libs, fused):
         assert p.exitcode == 0
     for _, err in results:
         assert err <= 1e-2
+
+
+def _worker_k(rank, world, port, q):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from oracle import w2a8_oracle as O
+        from slimkernels_b200 import workloads as W
+        from slimkernels_b200.torch.sharded import KShardedW2A8Gemm, shard_weight_k
+        M, N, K, G = 256, 512, 2048, 128
+        x_q, _, w_packed, w_scale = W.make_problem(M, N, K, G, seed=2)
+        scales = np.random.default_rng(9).uniform(0.005, 0.02, size=(world, M)).astype(np.float32)
+        per = K // world
+        wl, sl = shard_weight_k(torch.from_numpy(w_packed).to(dev), torch.from_numpy(w_scale).to(dev), world, rank, G)
+        op = KShardedW2A8Gemm(wl, sl, group_size=G)
+        xl = torch.from_numpy(np.ascontiguousarray(x_q[:, rank * per:(rank + 1) * per])).to(dev)
+        xs = torch.from_numpy(scales[rank]).to(dev)
+        mine = op(xl, xs)
+        full = op.forward_full(xl, xs)
+        torch.cuda.synchronize(dev)
+        ref = sum(O.w2a8_gemm_dequant_path(np.ascontiguousarray(x_q[:, r * per:(r + 1) * per]), scales[r],
+                                           np.ascontiguousarray(w_packed[:, r * per // 4:(r + 1) * per // 4]),
+                                           w_scale[r * per // G:(r + 1) * per // G], G) for r in range(world))
+        rows = M // world
+        q.put((rank, float(np.abs(mine.float().cpu().numpy() - ref[rank * rows:(rank + 1) * rows]).max()),
+               float(np.abs(full.float().cpu().numpy() - ref).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_k_sharded_reduce_scatter(built_libs):
+    """K-sharded down-projection style GEMM: partial products on each GPU, reduce-scatter by token rows."""
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_k, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for _, err_mine, err_full in results:
+        assert err_mine <= 1e-2 and err_full <= 1e-2
