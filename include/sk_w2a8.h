@@ -129,7 +129,7 @@ int sk_w2a8_quantize_weight(const float* w, int64_t ld_w, int64_t K, int64_t N, 
 int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int64_t K, int8_t* x_q, int64_t ld_q,
                                 float* x_scale, sk_stream_t stream);
 /* gate_up fp16 [M, ld_gu] (gate = columns [0, I), up = [I, 2I)) -> h = SiLU(gate) * up in fp32, quantised as
- * above to h_q int8 [M, ld_q], h_scale fp32 [M].  I % 8 == 0, I <= 51200. */
+ * above to h_q int8 [M, ld_q], h_scale fp32 [M].  I % 8 == 0. */
 int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M, int64_t I, int8_t* h_q,
                               int64_t ld_q, float* h_scale, sk_stream_t stream);
 /* The whole block: quantise x, W2A8 GEMM with the fused gate+up weight ([2I, hidden] packed, gate rows first),

@@ -129,4 +129,47 @@ silu_mul_quantize_kernel(const __half* __restrict__ gate_up, long long ld_gu, in
   }
 }
 
+// Same result for long rows, where the fp32 row in shared memory (4 * I bytes) would leave one CTA per SM: the row is
+// read twice instead (the second pass is an L2 hit) and SiLU(gate) * up is recomputed, which gives the identical
+// fp32 values; no dynamic shared memory, so eight CTAs fit an SM.
+__global__ void __launch_bounds__(kActThreads)
+silu_mul_quantize_twopass_kernel(const __half* __restrict__ gate_up, long long ld_gu, int8_t* __restrict__ h_q,
+                                 long long ld_q, float* __restrict__ h_scale, int I) {
+  __shared__ float red[kActThreads / 32];
+  const long long m = blockIdx.x;
+  const uint4* g = reinterpret_cast<const uint4*>(gate_up + m * ld_gu);
+  const uint4* u = reinterpret_cast<const uint4*>(gate_up + m * ld_gu + I);
+  const int nvec = I / 8;
+  auto silu_mul8 = [](const uint4& gv, const uint4& uv, float (&h)[8]) {
+    const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+    const __half2* uh = reinterpret_cast<const __half2*>(&uv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 gf = __half22float2(gh[j]), uf = __half22float2(uh[j]);
+      h[2 * j] = (gf.x / (1.f + expf(-gf.x))) * uf.x;
+      h[2 * j + 1] = (gf.y / (1.f + expf(-gf.y))) * uf.y;
+    }
+  };
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kActThreads) {
+    float h[8];
+    silu_mul8(g[v], u[v], h);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(h[j]));
+  }
+  amax = block_max(amax, red);
+  const float s = amax > 0.f ? amax / 127.f : 1.f;
+  if (threadIdx.x == 0) h_scale[m] = s;
+  uint2* qrow = reinterpret_cast<uint2*>(h_q + m * ld_q);
+  for (int v = threadIdx.x; v < nvec; v += kActThreads) {
+    float h[8];
+    silu_mul8(g[v], u[v], h);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j >> 2] |= (static_cast<uint32_t>(quantize_one(h[j], s)) & 0xffu) << (8 * (j & 3));
+    qrow[v] = make_uint2(w[0], w[1]);
+  }
+}
+
 }  // namespace sk

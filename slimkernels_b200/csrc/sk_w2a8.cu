@@ -794,25 +794,18 @@ int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int6
 int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M, int64_t I, int8_t* h_q, int64_t ld_q,
                               float* h_scale, sk_stream_t stream) {
   if (!gate_up_f16 || !h_q || !h_scale) return SK_ERR_NULL_POINTER;
-  if (M <= 0 || I <= 0 || (I % 8) != 0 || ld_gu < 2 * I || ld_q < I || M > 0x7fffffffLL) return SK_ERR_BAD_SHAPE;
-  if (4 * I > 200 * 1024) return SK_ERR_BAD_SHAPE;   // the fp32 row is kept in shared memory
+  if (M <= 0 || I <= 0 || (I % 8) != 0 || ld_gu < 2 * I || ld_q < I || M > 0x7fffffffLL || I > 0x7fffffffLL)
+    return SK_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(gate_up_f16) & 15) || (ld_gu % 8) || (reinterpret_cast<uintptr_t>(h_q) & 7) || (ld_q % 8))
     return SK_ERR_BAD_ALIGNMENT;
-  const int smem = static_cast<int>(4 * I);
-  if (smem > 48 * 1024) {
-    // per device, once: allow the larger dynamic shared memory window
-    static bool configured[64] = {false};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return SK_ERR_CUDA;
-    if (dev < 64 && !configured[dev]) {
-      if (cudaFuncSetAttribute(sk::silu_mul_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
-          cudaSuccess)
-        return SK_ERR_CUDA;
-      configured[dev] = true;
-    }
-  }
-  sk::silu_mul_quantize_kernel<<<static_cast<unsigned>(M), sk::kActThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(gate_up_f16), ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
+  const auto st = static_cast<cudaStream_t>(stream);
+  const __half* gu = static_cast<const __half*>(gate_up_f16);
+  if (4 * I <= 24 * 1024)    // short rows: the fp32 row stays in shared memory between the two passes (>= 8 CTAs per SM)
+    sk::silu_mul_quantize_kernel<<<static_cast<unsigned>(M), sk::kActThreads, static_cast<int>(4 * I), st>>>(
+        gu, ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
+  else                       // long rows: read twice and recompute (same values), full occupancy
+    sk::silu_mul_quantize_twopass_kernel<<<static_cast<unsigned>(M), sk::kActThreads, 0, st>>>(
+        gu, ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
   if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
   return SK_OK;
 }

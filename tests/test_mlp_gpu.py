@@ -37,7 +37,7 @@ def test_quantize_activation_bit_exact(M, K):
     np.testing.assert_array_equal(d_q.cpu().numpy(), q_ref)
 
 
-@pytest.mark.parametrize("M,I", [(1, 11008), (16, 11008), (9, 128), (4, 28672)])
+@pytest.mark.parametrize("M,I", [(1, 11008), (16, 11008), (9, 128), (4, 28672), (3, 6144), (3, 6152), (2, 60000)])
 def test_silu_mul_quantize(M, I):
     rng = np.random.default_rng(M + I)
     gu = (rng.standard_normal((M, 2 * I)) * 3).astype(np.float16)
