@@ -287,6 +287,52 @@ def side_kernels_sweep(dev, peaks):
     return out
 
 
+def mlp_block_sweep(dev, peaks):
+    """Benchmark config 4: the Llama-2-7B MLP block (hidden 4096, intermediate 11008) through W2A8LlamaMLP: token
+    quantiser, fused gate+up GEMM, SiLU*up + re-quantiser, down GEMM (four launches), fp16 in and out.  Also the
+    Llama-3-70B down projection of config 3 on one GPU (M=4096, N=8192, K=28672)."""
+    import torch
+    from slimkernels_b200.torch import W2A8Linear, W2A8LlamaMLP, W2A8Plan
+    rng = np.random.default_rng(0)
+    H, I, G = 4096, 11008, 128
+    st = torch.cuda.current_stream(dev)
+
+    def rand_linear(N, K):
+        wp = torch.from_numpy(rng.integers(0, 256, size=(N, K // 4), dtype=np.uint8)).to(dev)
+        ws = torch.from_numpy(rng.uniform(0.001, 0.01, size=(K // G, N)).astype(np.float16)).to(dev)
+        return W2A8Linear(wp, ws, group_size=G)
+
+    mlp = W2A8LlamaMLP(rand_linear(2 * I, H), rand_linear(H, I))
+    out = {"block": [], "llama3_70b_down": None}
+    wbytes = (2 * I * H + H * I) // 4 + ((H // G) * 2 * I + (I // G) * H) * 2
+    for M in (1, 16, 512, 4096):
+        x = torch.randn(M, H, device=dev, dtype=torch.float16)
+        for _ in range(3):
+            mlp(x)
+        torch.cuda.synchronize(dev)
+        ms = time_events(lambda: mlp(x), 30 if M <= 512 else 10, st)
+        ops = 6.0 * M * H * I
+        out["block"].append({"M": M, "us": round(ms * 1e3, 2), "tops": round(ops / (ms * 1e-3) / 1e12, 2),
+                             "weight_gbs_l2_warm": round(wbytes / (ms * 1e-3) / 1e9, 1)})
+    del mlp
+    N, K, M = 8192, 28672, 4096
+    lin = rand_linear(N, K)
+    x_q = torch.from_numpy(rng.integers(-127, 128, size=(M, K), dtype=np.int8)).to(dev)
+    xs = torch.from_numpy(rng.uniform(0.005, 0.02, size=(M,)).astype(np.float32)).to(dev)
+    y = torch.empty(M, N, dtype=torch.float16, device=dev)
+    plan = lin.plan()
+    for _ in range(3):
+        plan.gemm(x_q, xs, out=y)
+    torch.cuda.synchronize(dev)
+    ms = time_events(lambda: plan.gemm(x_q, xs, out=y), 10, st)
+    tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    out["llama3_70b_down"] = {"M": M, "N": N, "K": K, "us": round(ms * 1e3, 2), "tops": round(tops, 1),
+                              "frac_of_2x_bf16_burst": round(tops / (2 * peaks["bf16_tflops"]), 4)}
+    del lin, plan
+    torch.cuda.empty_cache()
+    return out
+
+
 def prefill_sweep(dev, peaks):
     import torch
     from slimkernels_b200 import workloads as W
@@ -445,6 +491,7 @@ def run_ours(args):
         line["prefill_sweep"] = pre
         line["library_int8_gemm_tops_8192"] = None if lib_tops is None else round(lib_tops, 1)
         line["side_kernels"] = side_kernels_sweep(dev, peaks)
+        line["mlp_block"] = mlp_block_sweep(dev, peaks)
     if world == 1 and rank == 0:
         line["cpu_baseline"] = run_cpu_baseline()
     if rank == 0:
