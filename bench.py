@@ -4,8 +4,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-sweeps]
 
 Headline workload (every N): the Llama-3-70B fused gate+up projection, M=4096 tokens, N=57344, K=8192,
-group 128, fp16 output; weights N-sharded over the ranks, fp16 output all-gathered with NCCL ("strong"
-scaling: total work fixed).  One step = one GEMM (+ all-gather when N > 1).  value = 2*M*N*K / time.
+group 128, fp16 output; weights N-sharded over the ranks, fp16 output all-gathered ("strong" scaling: total work
+fixed).  One step = one GEMM (+ all-gather when N > 1).  value = 2*M*N*K / time.  Outside the timed region every
+rank compares sampled output columns of every rank's slice with the CPU oracle and the integer partial sums of a
+sampled tile bit-exactly ("parity"); a failed check makes the run exit non-zero.  The down projection of the same
+benchmark config (N=8192, K=28672) and the other exchange variant are reported under "config3".
 
 At N=1 rank 0 additionally reports (outside the timed region) the decode sweep (Llama-2-7B shapes,
 M in {1,4,8,16,32}, HBM GB/s over packed-weight + scale bytes) and the prefill sweep (M in {2048,4096,8192},
@@ -32,6 +35,7 @@ if ROOT not in sys.path:
 METRIC = "w2a8_gemm_tops"
 UNIT = "TOPS"
 WORKLOAD = dict(name="llama3_70b_gate_up_prefill", M=4096, N=57344, K=8192, G=128)
+WORKLOAD_DOWN = dict(name="llama3_70b_down_prefill", M=4096, N=8192, K=28672, G=128)
 
 
 def read_peaks():
@@ -175,11 +179,12 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def config_dict(n_gpus):
+def config_dict(n_gpus, fused=True):
+    how = "peer stores in the GEMM epilogue over NVLink" if fused else "NCCL all_gather after the GEMM"
     return {"workload": f"{WORKLOAD['name']}: M={WORKLOAD['M']} N={WORKLOAD['N']} K={WORKLOAD['K']} G={WORKLOAD['G']} "
                         f"int8 x 2-bit -> fp16, seed 0 synthetic (benchmark config 3, gate+up)",
-            "parallelism": (f"N-sharded x{n_gpus}, output all-gathered (peer stores in the GEMM epilogue over NVLink; "
-                            f"--nccl-gather selects NCCL all_gather after the GEMM)") if n_gpus > 1 else "single GPU",
+            "parallelism": (f"N-sharded x{n_gpus}, output all-gathered ({how}; --nccl-gather selects the NCCL "
+                            f"exchange)") if n_gpus > 1 else "single GPU",
             "l2": "inputs larger than L2 (weights 117 MB + activations 34 MB + output 470 MB per step)"}
 
 
@@ -372,12 +377,205 @@ def prefill_sweep(dev, peaks):
     return out, lib_tops
 
 
-def run_ours(args):
+def kernel_description(plan, M):
+    """Names the kernel the plan launches for M tokens, from sk_w2a8_query_launch (nothing is assumed here)."""
+    q = plan.query_launch(M)
+    kind = {1: "w2a8_umma_kernel (tcgen05.mma kind::i8, weights expanded to int8 in shared memory)",
+            2: "w2a8_simt_kernel (CUDA cores)",
+            3: "w2a8_decode_kernel (tcgen05.mma kind::i8, weights expanded into tensor memory)",
+            4: "w2a8_pair_kernel (tcgen05.mma cta_group::2 kind::i8, two CTAs share one token tile)"}.get(q["kernel"], "?")
+    return f"{kind}: token tile {q['token_tile']}, split-K {q['split_k']}, {q['ctas']} CTAs", q
+
+
+def measured_traffic_ratio():
+    """dram read bytes / algorithmic read bytes of the prefill kernel, from the ncu capture summarised under profiles/."""
+    path = os.path.join(ROOT, "profiles", "w2a8_umma_prefill_M4096_N8192_K8192.json")
+    try:
+        d = json.load(open(path))
+        return float(d["dram_bytes_read"]) / float(d["algorithmic_bytes_read"]), os.path.relpath(path, ROOT)
+    except Exception:
+        return None, None
+
+
+def rank_weights(seed, rank, n_local, K, G):
+    """The slice of rank `rank`: every rank can re-draw any rank's slice on the host (the parity check needs columns of
+    all slices)."""
+    rng = np.random.default_rng([seed, rank])
+    wp = rng.integers(0, 256, size=(n_local, K // 4), dtype=np.uint8)
+    ws = rng.uniform(0.001, 0.01, size=(K // G, n_local)).astype(np.float16)
+    return wp, ws
+
+
+def parity_check(y_full, x_q_np, x_scale_np, wl, world, rank, seed, plan_cls, dev, local_wp, local_ws, cols_total=64):
+    """Outside the timed region: sampled output columns spread over every rank's slice against the CPU oracle (the
+    reference route: unpack -> dequantise -> fp32 matmul), and the per-group int32 partial sums of one sampled
+    128-feature tile x 256 tokens of this rank's slice bit-exactly."""
+    import torch
+    from oracle import w2a8_oracle as O
+    M, N, K, G = wl["M"], wl["N"], wl["K"], wl["G"]
+    n_local = N // world
+    per = max(1, cols_total // world)
+    rs = np.random.default_rng([seed, 1234])
+    max_err, checked = 0.0, 0
+    for q in range(world):
+        wp_q, ws_q = rank_weights(seed, q, n_local, K, G)
+        cols = np.sort(rs.choice(n_local, size=per, replace=False))
+        ref = O.w2a8_gemm_dequant_path(x_q_np, x_scale_np, np.ascontiguousarray(wp_q[cols]),
+                                       np.ascontiguousarray(ws_q[:, cols]), G)
+        got = y_full[:, torch.from_numpy(q * n_local + cols).to(y_full.device)].float().cpu().numpy()
+        max_err = max(max_err, float(np.abs(got - ref).max()))
+        checked += per
+        del wp_q, ws_q
+    # integer partial sums of one tile of this rank's slice, through the same kernel variant (256-token tile)
+    t0 = int(rs.integers(0, n_local // 128)) * 128
+    rows = torch.arange(t0, t0 + 128, device=dev)
+    sub = plan_cls(local_wp[rows].contiguous(), local_ws[:, rows].contiguous(), group_size=G)
+    mt = min(M, 256)
+    xq_d = torch.from_numpy(x_q_np[:mt]).to(dev)
+    p = sub.partials(xq_d).cpu().numpy()
+    wp_r, _ = rank_weights(seed, rank, n_local, K, G)
+    p_ref = O.w2a8_partials(x_q_np[:mt], np.ascontiguousarray(wp_r[t0:t0 + 128]), G)
+    exact = bool(np.array_equal(p, p_ref))
+    return {"max_abs_err": max_err, "partials_exact": exact, "cols_checked": checked, "tol": 1e-2,
+            "partials_checked": f"[{K // G} groups, {mt} tokens, features {rank * n_local + t0}..+128]"}
+
+
+def measure_workload(wl, seed, args, dev, world, rank, fused, steps, peaks, with_e2e=False, with_parity=True):
+    """One N-sharded GEMM (+ exchange) workload: device-timed step (max over ranks), this rank's GEMM alone (warmed,
+    min / median / max over ranks), exchange figures, parity.  Returns a dict (same on every rank)."""
     import torch
     import torch.distributed as dist
     from slimkernels_b200 import workloads as W
-    from slimkernels_b200.torch import load_extension
+    from slimkernels_b200.torch import W2A8Plan
     from slimkernels_b200.torch.sharded import ShardedW2A8Gemm, shard_bounds
+
+    M, N, K, G = wl["M"], wl["N"], wl["K"], wl["G"]
+    lo, hi = shard_bounds(N, world, rank)
+    n_local = hi - lo
+    wp_np, ws_np = rank_weights(seed, rank, n_local, K, G)
+    wp, ws = torch.from_numpy(wp_np).to(dev), torch.from_numpy(ws_np).to(dev)
+    del wp_np, ws_np
+    x_q_np, x_scale_np = W.make_activation(M, K, seed=seed)        # replicated activations
+    h_x = torch.from_numpy(x_q_np).pin_memory()
+    h_xs = torch.from_numpy(x_scale_np).pin_memory()
+    d_x, d_xs = h_x.to(dev), h_xs.to(dev)
+    op = ShardedW2A8Gemm(wp, ws, N, group_size=G, fused=fused)
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def over_ranks(ms):
+        if world == 1:
+            return ms, ms, ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        g = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(g, t)
+        v = sorted(float(a.item()) for a in g)
+        return v[0], v[len(v) // 2], v[-1]
+
+    for _ in range(max(args.warmup, 3)):
+        y = op(d_x, d_xs)
+    barrier()
+    with ClockSampler(dev.index) as clk:
+        barrier()
+        ms_step = time_events(lambda: op(d_x, d_xs), steps, stream)
+        barrier()
+    ms_step = over_ranks(ms_step)[2]
+    clocks = clk.summary()
+    res = {"workload": wl["name"], "M": M, "N": N, "K": K, "ms_per_step": round(ms_step, 4),
+           "tops": round(2.0 * M * N * K / (ms_step * 1e-3) / 1e12, 2), "steps": steps, "clocks": clocks,
+           "exchange": "none" if world == 1 else ("peer stores in the GEMM epilogue" if fused else "NCCL all-gather after the GEMM")}
+
+    # this rank's GEMM alone: same plan, its own [M, N_local] buffer made and warmed BEFORE the timed loop
+    for _ in range(3):
+        op.local_gemm(d_x, d_xs)
+    barrier()
+    ms_g = time_events(lambda: op.local_gemm(d_x, d_xs), steps, stream)
+    barrier()
+    g_min, g_med, g_max = over_ranks(ms_g)
+    desc, q = kernel_description(op.plan, M)
+    res["gemm_only"] = {"ms_min": round(g_min, 4), "ms_median": round(g_med, 4), "ms_max": round(g_max, 4),
+                        "tops_whole_job": round(2.0 * M * N * K / (g_max * 1e-3) / 1e12, 2), "kernel": desc}
+    res["_launch"] = q
+    res["_ms_kernel"] = g_max if world > 1 else ms_step
+    res["_n_local"] = n_local
+
+    if world > 1:
+        sent = (world - 1) * M * n_local * 2                       # bytes this rank must deliver to (and receive from) its peers
+        # link peak measured in the same run: NCCL all-gather of the same bytes (bus bandwidth = bytes received per
+        # rank / time = the per-direction rate the links sustain for this exchange pattern)
+        src = torch.empty(M, n_local, dtype=torch.float16, device=dev)
+        dst = torch.empty(world * M, n_local, dtype=torch.float16, device=dev)
+        for _ in range(3):
+            dist.all_gather_into_tensor(dst, src)
+        barrier()
+        ms_ag = over_ranks(time_events(lambda: dist.all_gather_into_tensor(dst, src), max(5, steps // 2), stream))[2]
+        barrier()
+        peak_gbs = sent / (ms_ag * 1e-3) / 1e9
+        del src, dst
+        link_bound_ms = sent / (peak_gbs * 1e9) * 1e3
+        bound_ms = max(link_bound_ms, g_max)
+        res["exchange_figures"] = {
+            "bytes_sent_per_rank": sent, "bytes_received_per_rank": sent,
+            "achieved_gbs_per_direction": round(sent / (ms_step * 1e-3) / 1e9, 1),
+            "link_peak_gbs_per_direction_measured": round(peak_gbs, 1),
+            "link_peak_how": f"NCCL all_gather_into_tensor of the same {sent} received bytes per rank in this run: {round(ms_ag, 4)} ms",
+            "link_bound_ms": round(link_bound_ms, 4), "gemm_bound_ms": round(g_max, 4),
+            "step_over_bound": round(ms_step / bound_ms, 3),
+            "frac_of_bound": round(bound_ms / ms_step, 4),
+            "note": "a gather that lands the whole [M, N] on every rank cannot finish before max(link_bound_ms, gemm_bound_ms)"}
+
+    if with_parity:
+        y = op(d_x, d_xs)
+        torch.cuda.synchronize(dev)
+        par = parity_check(y, x_q_np, x_scale_np, wl, world, rank, seed, W2A8Plan, dev, wp, ws,
+                           cols_total=64 if K <= 8192 else 32)
+        if world > 1:
+            t = torch.tensor([par["max_abs_err"], 0.0 if par["partials_exact"] else 1.0], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            par["max_abs_err"], par["partials_exact"] = float(t[0].item()), bool(t[1].item() == 0.0)
+            par["ranks_checked"] = world
+        par["max_abs_err"] = round(par["max_abs_err"], 6)
+        par["ok"] = bool(par["max_abs_err"] <= par["tol"] and par["partials_exact"])
+        res["parity"] = par
+
+    if with_e2e:
+        h_out = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
+
+        def e2e_step():
+            if world == 1:
+                op.plan.gemm_host(h_x, h_xs, h_out)   # the host-buffer call of the public API: copies and GEMM chunks overlap
+                return
+            d_x.copy_(h_x, non_blocking=True)
+            d_xs.copy_(h_xs, non_blocking=True)
+            yy = op(d_x, d_xs)
+            h_out.copy_(yy[:, lo:hi], non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e2e_steps = max(2, min(steps, 10))
+        ms_e2e = over_ranks(time_events(e2e_step, e2e_steps, stream))[2]
+        barrier()
+        res["e2e"] = {"value": round(2.0 * M * N * K / (ms_e2e * 1e-3) / 1e12, 3), "unit": UNIT,
+                      "h2d_bytes_per_step": int(world * (h_x.numel() + h_xs.numel() * 4)),
+                      "d2h_bytes_per_step": int(M * N * 2), "ms_per_step": round(ms_e2e, 4),
+                      "note": "per step: activations H2D from pinned memory on every rank, GEMM (+ all-gather), each rank's "
+                              "output slice D2H; on one GPU through W2A8Plan.gemm_host (token chunks, copies and GEMMs "
+                              "overlapped on three streams)"}
+        del h_out
+    del op, wp, ws, d_x, d_xs, h_x, h_xs
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from slimkernels_b200.torch import load_extension
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device visible; the W2A8 path has no CPU fallback")
@@ -390,102 +588,59 @@ def run_ours(args):
             raise SystemExit("bench.py: --gpus N > 1 must be launched with torch.distributed.run")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     peaks = read_peaks()
+    fused = world > 1 and not args.nccl_gather
 
+    # ---- headline workload: timed region of K steps with device-resident inputs, then e2e and parity
+    head = measure_workload(WORKLOAD, 0, args, dev, world, rank, fused, args.steps, peaks, with_e2e=True)
     M, N, K, G = WORKLOAD["M"], WORKLOAD["N"], WORKLOAD["K"], WORKLOAD["G"]
-    lo, hi = shard_bounds(N, world, rank)
-    n_local = hi - lo
-    rng_w = np.random.default_rng([0, rank])                    # each rank draws its own slice
-    wp = torch.from_numpy(rng_w.integers(0, 256, size=(n_local, K // 4), dtype=np.uint8)).to(dev)
-    ws = torch.from_numpy(rng_w.uniform(0.001, 0.01, size=(K // G, n_local)).astype(np.float16)).to(dev)
-    x_q_np, x_scale_np = W.make_activation(M, K, seed=0)        # replicated activations
-    h_x = torch.from_numpy(x_q_np).pin_memory()
-    h_xs = torch.from_numpy(x_scale_np).pin_memory()
-    d_x, d_xs = h_x.to(dev), h_xs.to(dev)
-    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-    op = ShardedW2A8Gemm(wp, ws, N, group_size=G, fused=(world > 1 and not args.nccl_gather))
-    h_out = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
-    stream = torch.cuda.current_stream(dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- warm-up
-    for _ in range(max(args.warmup, 3)):
-        op(d_x, d_xs)
-    barrier()
-
-    # ---- timed region: K steps, device-resident inputs
-    with ClockSampler(local_rank) as clk:
-        barrier()
-        ms_step = time_events(lambda: op(d_x, d_xs), args.steps, stream)
-        barrier()
-    ms_step = max_over_ranks(ms_step)
-    clocks = clk.summary()
-    value = 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
-
-    # ---- dominant kernel alone (this rank's GEMM launch), CUDA events on the launching stream
-    # (on one GPU the step IS that launch: the timed region above is the measurement; with several GPUs the step also
-    # holds the exchange, so the rank's GEMM is timed again on its own)
-    barrier()
-    ms_kernel = ms_step if world == 1 else max_over_ranks(time_events(lambda: op.local_gemm(d_x, d_xs), args.steps, stream))
+    n_local = head["_n_local"]
+    ms_kernel = head["_ms_kernel"]
     tops_kernel = 2.0 * M * n_local * K / (ms_kernel * 1e-3) / 1e12
     peak_int8 = 2.0 * peaks["bf16_tflops"]
-    groups = K // G
-    traffic = n_local * K // 4 + groups * n_local * 2 + M * K + M * 4 + M * n_local * 2
+    alg_read = n_local * K // 4 + (K // G) * n_local * 2 + M * K + M * 4
+    alg_write = M * n_local * 2
+    ratio, ratio_src = measured_traffic_ratio()
+    traffic = int((ratio or 1.0) * alg_read + alg_write)
     roofline = {"bound": "tensor", "achieved": round(tops_kernel, 2), "peak": round(peak_int8, 1), "unit": "TOP/s",
                 "frac": round(tops_kernel / peak_int8, 4), "traffic": traffic,
-                "traffic_note": "algorithmic HBM bytes per launch (weights + scales + activations read once, output "
-                                "written once); the ncu capture of the M=4096 N=K=8192 case measured "
-                                "dram read = 1.06 x algorithmic (profiles/), this workload is too large to capture",
-                "kernel": "w2a8_umma_kernel<256,2,4,4,4,2> (tcgen05.mma kind::i8; token tile 256, one CTA per tile, two MMA-issuing warps)", "ms_per_launch": round(ms_kernel, 4),
+                "traffic_how": {"algorithmic_bytes_read": alg_read, "algorithmic_bytes_write": alg_write,
+                                "measured_read_over_algorithmic": ratio, "from": ratio_src,
+                                "note": "dram bytes of the ncu capture of the M=4096 N=K=8192 case, scaled by the bytes this "
+                                        "launch moves (this workload is too large to capture); writes counted once"},
+                "kernel": head["gemm_only"]["kernel"], "ms_per_launch": round(ms_kernel, 4),
+                "ms_per_launch_over_ranks": {k: head["gemm_only"][k] for k in ("ms_min", "ms_median", "ms_max")},
                 "peak_note": f"2 x {peaks['source']} bf16 burst TFLOP/s (no int8 figure is measured on this pool); "
                              f"vs 2 x sustained: {round(tops_kernel / (2 * peaks['bf16_tflops_sustained']), 4)}; "
                              f"vs nominal 4500: {round(tops_kernel / 4500.0, 4)}",
                 "algorithmic_ops_per_launch": 2.0 * M * n_local * K}
 
-    # ---- end to end: pinned host activations in, this rank's output slice back to the host, every step
-    def e2e_step():
-        if world == 1:
-            # the host-buffer call of the public API: copies and GEMM chunks overlap on three streams
-            op.plan.gemm_host(h_x, h_xs, h_out)
-            return
-        d_x.copy_(h_x, non_blocking=True)
-        d_xs.copy_(h_xs, non_blocking=True)
-        y = op(d_x, d_xs)
-        h_out.copy_(y[:, lo:hi], non_blocking=True)
-
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e2e_steps = max(2, min(args.steps, 10))
-    ms_e2e = max_over_ranks(time_events(e2e_step, e2e_steps, stream))
-    barrier()
-    e2e = {"value": round(2.0 * M * N * K / (ms_e2e * 1e-3) / 1e12, 3), "unit": UNIT,
-           "h2d_bytes_per_step": int(world * (h_x.numel() + h_xs.numel() * 4)),
-           "d2h_bytes_per_step": int(M * N * 2), "ms_per_step": round(ms_e2e, 4),
-           "note": "per step: activations H2D from pinned memory on every rank, GEMM (+ all-gather), each rank's output slice D2H; on one GPU through W2A8Plan.gemm_host (token chunks, copies and GEMMs overlapped on three streams)"}
-
-    line = {"metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+    line = {"metric": METRIC, "value": head["tops"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int2 -> int32 -> fp32 scale -> fp16",
-            "data": "synthetic", "config": config_dict(world), "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps, "roofline": roofline, "peaks": peaks}
+            "data": "synthetic", "config": config_dict(world, fused), "clocks": head["clocks"], "e2e": head["e2e"],
+            "gpu_launches": args.steps, "roofline": roofline, "peaks": peaks, "parity": head["parity"],
+            "gemm_only": head["gemm_only"]}
+    if world > 1:
+        line["exchange"] = head["exchange_figures"]
+
+    def strip(d):
+        return {k: v for k, v in d.items() if not k.startswith("_")}
+
+    # ---- the other GEMM of benchmark config 3 (down projection, N-sharded the same way) and the other exchange
+    if not args.no_sweeps or world > 1:
+        few = max(3, min(args.steps, 10))
+        extra = {}
+        extra["down_proj"] = strip(measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, fused, few, peaks))
+        if world > 1:
+            extra["gate_up_other_exchange"] = strip(measure_workload(WORKLOAD, 0, args, dev, world, rank, not fused, few, peaks))
+            extra["down_proj_other_exchange"] = strip(measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, not fused, few, peaks))
+        line["config3"] = extra
 
     if world == 1 and not args.no_sweeps:
-        del op, wp, ws
-        torch.cuda.empty_cache()
         line["decode_sweep"] = decode_sweep(dev, peaks)
         pre, lib_tops = prefill_sweep(dev, peaks)
         line["prefill_sweep"] = pre
@@ -494,11 +649,15 @@ def run_ours(args):
         line["mlp_block"] = mlp_block_sweep(dev, peaks)
     if world == 1 and rank == 0:
         line["cpu_baseline"] = run_cpu_baseline()
+    ok = line["parity"]["ok"] and all(v.get("parity", {"ok": True})["ok"] for v in line.get("config3", {}).values())
+    line["parity_all_ok"] = bool(ok)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("bench.py: parity check failed (see the \"parity\" keys of the line above)")
 
 
 def main():

@@ -66,8 +66,14 @@ typedef enum sk_option {
   SK_OPT_DEPENDENT_LAUNCH = 5, /* decode kernel: 0 auto (2 when the grid has more CTAs than the GPU has SMs, else 1),
                              1 plain launch, 2 programmatic dependent launch: the kernel's set-up and first weight
                              copies overlap the tail of the previous kernel in the stream */
-  SK_OPT_PERSISTENT = 4   /* 0 auto (= 1), 1 one CTA per tile, 2 one resident set of CTAs walks all tiles (token tiles
+  SK_OPT_PERSISTENT = 4,  /* 0 auto (= 1), 1 one CTA per tile, 2 one resident set of CTAs walks all tiles (token tiles
                              128 / 256 without split-K, when there are more tiles than the GPU holds at once) */
+  SK_OPT_WAIT_LIMIT_CYCLES = 7, /* SM cycles after which a wait inside a kernel gives up and the kernel returns with a
+                             device status (0 = default, 1e9 cycles, about half a second; otherwise >= 1000) */
+  SK_OPT_TEST_SKIP_COPY = 8 /* failure-path test hook, 0 = off: with value v > 0 the producer of every CTA leaves out
+                             the copies of K block v - 1 of its range, so the waits for them run into the limit, the
+                             kernel returns and sk_w2a8_last_device_status reports which wait gave up.  The output
+                             of such a launch is undefined.  Nothing traps or faults. */
 } sk_option;
 
 /* -------- weight preparation ("Blackwell tile order") ------------------------------------------
@@ -90,6 +96,9 @@ int sk_w2a8_plan_create(sk_w2a8_plan** plan, int device, int64_t N, int64_t K, i
                         int out_dtype);
 int sk_w2a8_plan_destroy(sk_w2a8_plan* plan);
 int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value);
+/* What the plan was created with (any out-pointer may be NULL). */
+int sk_w2a8_plan_info(const sk_w2a8_plan* plan, int64_t* N, int64_t* K, int* group_size, int* zero_point,
+                      int* out_dtype, int* device);
 
 /* -------- the GEMM (replaces gemm_tn, wgmma_sm90_W2A8.cu:428-506) ---------------------------------
  * Stream-ordered and asynchronous; no allocation, no synchronisation. */
@@ -164,6 +173,8 @@ int sk_w2a8_mlp_forward_static(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_
 /* Synchronously reads (and clears) the plan's device status word: 0, or a code naming the wait that
  * expired inside the kernel (role * 16 + barrier kind).  Non-zero maps to SK_ERR_DEVICE_TIMEOUT. */
 int sk_w2a8_last_device_status(sk_w2a8_plan* plan, int* device_status);
+/* Names the role and the wait behind a device status code (static string). */
+const char* sk_device_status_string(int device_status);
 int sk_w2a8_last_cuda_error(const sk_w2a8_plan* plan);
 /* Describes the launch the plan would make for M tokens: token tile, split-K factor, CTAs, kernel kind. */
 int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* split_k, int* ctas,

@@ -25,6 +25,7 @@ SK_ERR_STATIC_SCRATCH_TOO_SMALL = -10
 SK_OUT_F16, SK_OUT_BF16 = 0, 1
 SK_WEIGHT_ROWMAJOR, SK_WEIGHT_TILED = 0, 1
 SK_OPT_KERNEL, SK_OPT_TOKEN_TILE, SK_OPT_SPLIT_K, SK_OPT_PERSISTENT, SK_OPT_DEPENDENT_LAUNCH, SK_OPT_TMA_STORE = 1, 2, 3, 4, 5, 6
+SK_OPT_WAIT_LIMIT_CYCLES, SK_OPT_TEST_SKIP_COPY = 7, 8
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_CUDA_CORE, KERNEL_TCGEN05_DECODE = 0, 1, 2, 3
 
 _i64, _int, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
@@ -37,6 +38,8 @@ SIGNATURES = {
     "sk_w2a8_plan_create": (_int, [ctypes.POINTER(_vp), _int, _i64, _i64, _int, _int, _vp, _int, _vp, _int]),
     "sk_w2a8_plan_destroy": (_int, [_vp]),
     "sk_w2a8_set_option": (_int, [_vp, _int, _i64]),
+    "sk_w2a8_plan_info": (_int, [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_int),
+                                 ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(_int)]),
     "sk_w2a8_gemm": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp]),
     "sk_w2a8_gemm_scatter": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.POINTER(_vp), _int, _i64, _i64, _vp]),
     "sk_w2a8_gemm_debug_partials": (_int, [_vp, _i64, _vp, _i64, _vp, _vp]),
@@ -49,6 +52,7 @@ SIGNATURES = {
     "sk_w2a8_mlp_forward_static": (_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "sk_w2a8_last_device_status": (_int, [_vp, ctypes.POINTER(_int)]),
     "sk_w2a8_last_cuda_error": (_int, [_vp]),
+    "sk_device_status_string": (ctypes.c_char_p, [_int]),
     "sk_w2a8_query_launch": (_int, [_vp, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(_int),
                                     ctypes.POINTER(_int)]),
     "sk_status_string": (ctypes.c_char_p, [_int]),
@@ -112,6 +116,9 @@ class Plan:
     def partials(self, M, x_q_ptr, ld_x, partials_ptr, stream=0) -> None:
         check(load().sk_w2a8_gemm_debug_partials(self._h, M, x_q_ptr, ld_x, partials_ptr, stream),
               "sk_w2a8_gemm_debug_partials")
+
+    def device_status_string(self, code: int) -> str:
+        return load().sk_device_status_string(code).decode()
 
     def device_status(self) -> int:
         v = _int(0)

@@ -166,6 +166,8 @@ struct sk_w2a8_plan {
   int* status = nullptr;                // device, owned
   int last_cuda_error = 0;
   int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0, opt_pdl = 0, opt_tma_store = 0;
+  long long opt_wait_limit = 0;         // 0: the default limit
+  int opt_skip_copy = 0;                // failure-path test hook: 1 + index of the K block whose copies are left out
   std::vector<sk::CachedMap> maps;      // small cache of activation tensor maps
   std::mutex mu;
 };
@@ -320,6 +322,25 @@ static bool running_sum_fits(const sk_w2a8_plan* plan, int token_tile, int split
   return k_per_buf * 127 * mx < (1LL << 22);
 }
 
+// The launch run_gemm makes for M tokens: the heuristic choice, then the depth check.  A K range too deep for the two
+// accumulator buffers of the 256-token tile falls back to 128 tokens (four buffers, half the depth per buffer);
+// beyond that the call is refused.
+static int resolve_launch(const sk_w2a8_plan* plan, long long M, bool debug_partials, LaunchChoice* out) {
+  LaunchChoice ch = choose(plan, M);
+  if (debug_partials) { ch.split_k = 1; ch.persistent = 0; }
+  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k, ch.kernel)) {
+    if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1, 1)) {
+      ch.token_tile = 128;
+      ch.persistent = 0;
+      ch.ctas = static_cast<int>(plan->n_tiles * ((M + 127) / 128));
+    } else {
+      return SK_ERR_BAD_SHAPE;   // K too deep for the int32 running sums of this tile configuration
+    }
+  }
+  *out = ch;
+  return SK_OK;
+}
+
 // partials[g] holds the running sum of its accumulator buffer; turn it into the group's own partial sum.
 __global__ void diff_partials_kernel(int32_t* __restrict__ partials, int groups, long long mn, int acc_bufs) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < mn;
@@ -419,13 +440,12 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
     e = cudaSetDevice(plan->device);
     if (e != cudaSuccess) return cuda_fail(plan, e);
   }
-  LaunchChoice ch = choose(plan, M);
-  if (partials) ch.split_k = 1;
-  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k, ch.kernel)) {
-    if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1, 1)) ch.token_tile = 128;
-    else return SK_ERR_BAD_SHAPE;   // K too deep for the int32 running sums of this tile configuration
+  LaunchChoice ch;
+  int rc = resolve_launch(plan, M, partials != nullptr, &ch);
+  if (rc != SK_OK) {
+    if (cur != plan->device) (void)cudaSetDevice(cur);
+    return rc;
   }
-  int rc = SK_OK;
   if (ch.kernel == 2) {
     if (!plan->w_rowmajor || n_extra > 0) rc = SK_ERR_UNAVAILABLE;
     else {
@@ -460,6 +480,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.groups = static_cast<int>(plan->K / plan->G);
       prm.zero_point = plan->zero_point;
       prm.out_bf16 = plan->out_dtype == SK_OUT_BF16;
+      prm.wait_limit = plan->opt_wait_limit > 0 ? plan->opt_wait_limit : kWaitLimitCycles;
+      prm.fault_skip_kb = plan->opt_skip_copy - 1;
 #ifdef SK_TRACE
       prm.trace = g_trace_buffer;
 #endif
@@ -669,6 +691,18 @@ int sk_w2a8_plan_destroy(sk_w2a8_plan* plan) {
   return SK_OK;
 }
 
+int sk_w2a8_plan_info(const sk_w2a8_plan* plan, int64_t* N, int64_t* K, int* group_size, int* zero_point,
+                      int* out_dtype, int* device) {
+  if (!plan) return SK_ERR_NULL_POINTER;
+  if (N) *N = plan->N;
+  if (K) *K = plan->K;
+  if (group_size) *group_size = plan->G;
+  if (zero_point) *zero_point = plan->zero_point;
+  if (out_dtype) *out_dtype = plan->out_dtype;
+  if (device) *device = plan->device;
+  return SK_OK;
+}
+
 int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
   if (!plan) return SK_ERR_NULL_POINTER;
   switch (key) {
@@ -698,6 +732,14 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
     case SK_OPT_PERSISTENT:
       if (value < 0 || value > 2) return SK_ERR_BAD_ARGUMENT;
       plan->opt_persistent = static_cast<int>(value);
+      return SK_OK;
+    case SK_OPT_WAIT_LIMIT_CYCLES:
+      if (value < 0 || (value != 0 && value < 1000)) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_wait_limit = value;
+      return SK_OK;
+    case SK_OPT_TEST_SKIP_COPY:
+      if (value < 0 || value > (1 << 20)) return SK_ERR_BAD_ARGUMENT;
+      plan->opt_skip_copy = static_cast<int>(value);
       return SK_OK;
     default: return SK_ERR_BAD_ARGUMENT;
   }
@@ -746,10 +788,27 @@ int sk_w2a8_last_device_status(sk_w2a8_plan* plan, int* device_status) {
 
 int sk_w2a8_last_cuda_error(const sk_w2a8_plan* plan) { return plan ? plan->last_cuda_error : 0; }
 
+const char* sk_device_status_string(int device_status) {
+  switch (device_status) {
+    case 0: return "no wait expired";
+    case sk::kStProducerEmpty: return "producer: a pipeline stage was never released by the MMAs that read it";
+    case sk::kStExpanderFull: return "expander: the copies of a pipeline stage never landed";
+    case sk::kStExpanderEmpty: return "expander: a buffer of expanded weights was never released by the MMAs that read it";
+    case sk::kStMmaLdFull: return "MMA issuer: the copies of a pipeline stage never landed";
+    case sk::kStMmaExFull: return "MMA issuer: the expanded weights of a stage never arrived";
+    case sk::kStMmaAccEmpty: return "MMA issuer: an accumulator buffer was never released by the epilogue";
+    case sk::kStEpilogueAccFull: return "epilogue: the MMAs of a scale group never completed";
+    case sk::kStDrain: return "producer: a copy in flight did not land while the CTA was giving up";
+    default: return "unknown device status";
+  }
+}
+
 int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* split_k, int* ctas, int* kernel_kind) {
   if (!plan) return SK_ERR_NULL_POINTER;
   if (M <= 0) return SK_ERR_BAD_SHAPE;
-  const sk::LaunchChoice c = sk::choose(plan, M);
+  sk::LaunchChoice c;
+  const int rc = sk::resolve_launch(plan, M, false, &c);
+  if (rc != SK_OK) return rc;
   if (token_tile) *token_tile = c.token_tile;
   if (split_k) *split_k = c.split_k;
   if (ctas) *ctas = c.ctas;
@@ -827,6 +886,7 @@ inline MlpLayout mlp_layout(int64_t M, int64_t hidden, int64_t inter) {
   l.total = o;
   return l;
 }
+// The caller has made the plans' device current: the two side kernels launch on the current device.
 int mlp_run(sk_w2a8_plan* gu, sk_w2a8_plan* down, int64_t M, const void* x, int64_t ld_x, void* out, int64_t ld_out,
             char* ws, sk_stream_t stream) {
   const int64_t hidden = gu->K, inter = down->K;
@@ -864,7 +924,14 @@ int sk_w2a8_mlp_forward(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_t M, co
   if (!x_f16 || !out || !workspace) return SK_ERR_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return SK_ERR_BAD_ALIGNMENT;
   if (workspace_bytes < static_cast<int64_t>(mlp_layout(M, gate_up->K, down->K).total)) return SK_ERR_BAD_SHAPE;
-  return mlp_run(gate_up, down, M, x_f16, ld_x, out, ld_out, static_cast<char*>(workspace), stream);
+  // a plan is bound to one device: run there whatever device the calling thread has current, and put that back
+  const int dev = gate_up->device;
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) return sk::cuda_fail(gate_up, cudaGetLastError());
+  if (cur != dev && cudaSetDevice(dev) != cudaSuccess) return sk::cuda_fail(gate_up, cudaGetLastError());
+  rc = mlp_run(gate_up, down, M, x_f16, ld_x, out, ld_out, static_cast<char*>(workspace), stream);
+  if (cur != dev) (void)cudaSetDevice(cur);
+  return rc;
 }
 
 // ------------------------------------------------------------------------------------------------

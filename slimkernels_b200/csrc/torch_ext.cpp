@@ -5,6 +5,9 @@
 #include <torch/library.h>
 #include <torch/types.h>
 
+#include <mutex>
+#include <vector>
+
 #include "../../include/sk_w2a8.h"
 
 namespace {
@@ -60,6 +63,13 @@ void gemm_out(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, 
   TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == M && out.stride(1) == 1,
               "out must be [M, N] with unit inner stride");
   TORCH_CHECK(out.scalar_type() == at::kHalf || out.scalar_type() == at::kBFloat16, "out must be float16 or bfloat16");
+  int64_t plan_n = 0, plan_k = 0;
+  int plan_dtype = 0, plan_dev = 0;
+  check(sk_w2a8_plan_info(as_plan(handle), &plan_n, &plan_k, nullptr, nullptr, &plan_dtype, &plan_dev), "w2a8_plan_info");
+  TORCH_CHECK(out.size(1) == plan_n && K == plan_k, "out must have N = ", plan_n, " columns and x_q K = ", plan_k);
+  TORCH_CHECK((out.scalar_type() == at::kBFloat16) == (plan_dtype == SK_OUT_BF16),
+              "out has dtype ", out.scalar_type(), " but the plan produces ", plan_dtype == SK_OUT_BF16 ? "bfloat16" : "float16");
+  TORCH_CHECK(out.get_device() == plan_dev && x_q.get_device() == plan_dev, "tensors must live on the plan's device ", plan_dev);
   if (M == 0) return;
   c10::cuda::CUDAGuard guard(x_q.device());
   auto stream = at::cuda::getCurrentCUDAStream();
@@ -167,6 +177,13 @@ at::Tensor mlp_forward(int64_t gate_up_plan, int64_t down_plan, const at::Tensor
   return out;
 }
 
+// [token tile, split-K, CTAs, kernel kind] of the launch the plan makes for M tokens
+std::vector<int64_t> query_launch(int64_t handle, int64_t M) {
+  int t = 0, sp = 0, c = 0, k = 0;
+  check(sk_w2a8_query_launch(as_plan(handle), M, &t, &sp, &c, &k), "w2a8_query_launch");
+  return {t, sp, c, k};
+}
+
 int64_t device_status(int64_t handle) {
   int v = 0;
   int rc = sk_w2a8_last_device_status(as_plan(handle), &v);
@@ -195,9 +212,89 @@ at::Tensor unrepack(const at::Tensor& w_tiled, int64_t N, int64_t K) {
   return out;
 }
 
+// ------------------------------------------------------------------------------------------------
+// The functional op.  Call shape of the reference's notebook wrapper  wint2_gemm(activation, weight, scale) -> out
+// (triton.ipynb:235-270): operands in, a fresh [M, N] tensor out, on the current stream.  The plan behind a weight
+// (its tiled copy) is made on first use and kept in a small cache that holds the weight tensors WEAKLY: an entry
+// dies with its tensors, and is rebuilt if they were written in place.
+// ------------------------------------------------------------------------------------------------
+struct CachedPlan {
+  c10::weak_intrusive_ptr<c10::TensorImpl> w, s;
+  const void* w_ptr;
+  const void* s_ptr;
+  int64_t w_version, s_version;
+  int64_t group_size, zero_point;
+  bool bf16;
+  sk_w2a8_plan* plan;
+};
+std::mutex g_cache_mu;
+std::vector<CachedPlan> g_cache;
+constexpr size_t kMaxCachedPlans = 512;
+
+sk_w2a8_plan* cached_plan(const at::Tensor& w_packed, const at::Tensor& w_scale, int64_t group_size, int64_t zero_point,
+                          bool bf16) {
+  TORCH_CHECK(w_packed.is_cuda() && w_packed.scalar_type() == at::kByte && w_packed.is_contiguous() && w_packed.dim() == 2,
+              "w_packed must be a contiguous 2-D CUDA uint8 tensor [N, K/4]");
+  const int64_t N = w_packed.size(0), K = w_packed.size(1) * 4;
+  std::lock_guard<std::mutex> lock(g_cache_mu);
+  sk_w2a8_plan* hit = nullptr;
+  for (size_t i = 0; i < g_cache.size();) {
+    CachedPlan& e = g_cache[i];
+    const bool dead = e.w.expired() || e.s.expired();
+    const bool same = !dead && e.w_ptr == w_packed.data_ptr() && e.s_ptr == w_scale.data_ptr() &&
+                      e.w.lock().get() == w_packed.unsafeGetTensorImpl() && e.s.lock().get() == w_scale.unsafeGetTensorImpl() &&
+                      e.group_size == group_size && e.zero_point == zero_point && e.bf16 == bf16;
+    const bool stale = same && (e.w_version != w_packed._version() || e.s_version != w_scale._version());
+    if (dead || stale) {
+      sk_w2a8_plan_destroy(e.plan);
+      g_cache[i] = g_cache.back();
+      g_cache.pop_back();
+      continue;
+    }
+    if (same) hit = e.plan;
+    ++i;
+  }
+  if (hit) return hit;
+  if (g_cache.size() >= kMaxCachedPlans) {      // oldest first
+    sk_w2a8_plan_destroy(g_cache.front().plan);
+    g_cache.erase(g_cache.begin());
+  }
+  const int64_t handle = plan_create(w_packed, w_scale, N, K, group_size, zero_point, bf16, /*tiled=*/false);
+  CachedPlan e{c10::weak_intrusive_ptr<c10::TensorImpl>(w_packed.getIntrusivePtr()),
+               c10::weak_intrusive_ptr<c10::TensorImpl>(w_scale.getIntrusivePtr()),
+               w_packed.data_ptr(), w_scale.data_ptr(), w_packed._version(), w_scale._version(),
+               group_size, zero_point, bf16, as_plan(handle)};
+  g_cache.push_back(e);
+  return e.plan;
+}
+
+at::Tensor w2a8_gemm_op(const at::Tensor& x_q, const at::Tensor& x_scale, const at::Tensor& w_packed,
+                        const at::Tensor& w_scale, int64_t group_size, int64_t zero_point, at::ScalarType out_dtype) {
+  TORCH_CHECK(out_dtype == at::kHalf || out_dtype == at::kBFloat16, "out_dtype must be float16 or bfloat16");
+  const bool bf16 = out_dtype == at::kBFloat16;
+  sk_w2a8_plan* plan = cached_plan(w_packed, w_scale, group_size, zero_point, bf16);
+  return gemm(static_cast<int64_t>(reinterpret_cast<intptr_t>(plan)), x_q, x_scale, w_packed.size(0), w_packed.size(1) * 4, bf16);
+}
+
+at::Tensor w2a8_partials_op(const at::Tensor& x_q, const at::Tensor& w_packed, const at::Tensor& w_scale,
+                            int64_t group_size, int64_t zero_point) {
+  sk_w2a8_plan* plan = cached_plan(w_packed, w_scale, group_size, zero_point, false);
+  return partials(static_cast<int64_t>(reinterpret_cast<intptr_t>(plan)), x_q, w_packed.size(0), w_packed.size(1) * 4, group_size);
+}
+
+int64_t cached_plan_count() {
+  std::lock_guard<std::mutex> lock(g_cache_mu);
+  size_t live = 0;
+  for (const auto& e : g_cache) live += !(e.w.expired() || e.s.expired());
+  return static_cast<int64_t>(live);
+}
+
 }  // namespace
 
 TORCH_LIBRARY(slimkernels, m) {
+  m.def("w2a8_gemm(Tensor x_q, Tensor x_scale, Tensor w_packed, Tensor w_scale, int group_size=128, int zero_point=1, ScalarType out_dtype=float16) -> Tensor", &w2a8_gemm_op);
+  m.def("w2a8_partials(Tensor x_q, Tensor w_packed, Tensor w_scale, int group_size=128, int zero_point=1) -> Tensor", &w2a8_partials_op);
+  m.def("w2a8_cached_plan_count() -> int", &cached_plan_count);
   m.def("w2a8_plan_create(Tensor w, Tensor w_scale, int N, int K, int group_size, int zero_point, bool bf16_out, bool tiled) -> int", &plan_create);
   m.def("w2a8_plan_destroy(int plan) -> ()", &plan_destroy);
   m.def("w2a8_plan_set_option(int plan, int key, int value) -> ()", &plan_set_option);
@@ -206,6 +303,7 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_gemm_scatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int ld_out, int col_offset, int K) -> ()", &gemm_scatter);
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
+  m.def("w2a8_plan_query_launch(int plan, int M) -> int[]", &query_launch);
   m.def("quantize_activation_int8(Tensor x) -> (Tensor, Tensor)", &quantize_activation);
   m.def("w2a8_quantize_weight(Tensor w_kn, int group_size) -> (Tensor, Tensor, Tensor)", &quantize_weight);
   m.def("silu_mul_quantize_int8(Tensor gate_up) -> (Tensor, Tensor)", &silu_mul_quantize);

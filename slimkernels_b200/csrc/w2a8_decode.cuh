@@ -90,7 +90,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   const uint32_t bar_acc_empty = bar_ex_full + 8u * T::kASubs;    // [2] the epilogue has read the accumulator set
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::kOffMisc + 4);
-  const WaitCtx ctx{abort_flag, p.status};
+  const WaitCtx ctx{abort_flag, p.status, p.wait_limit};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -142,6 +142,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     if (elect_one()) {
       const uint8_t* w = wsrc;
       for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
+        if (i == p.fault_skip_kb) continue;   // failure-path test hook: this stage is never filled
         const int n = min(T::kKbPerStage, nkb - i);
         const uint32_t full = bar_ld_full + 8 * st;
         SK_TRACE_EVENT(0, st);
@@ -154,6 +155,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     grid_dep_wait();
     if (elect_one()) {
       for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
+        if (i == p.fault_skip_kb) continue;
         const int n = min(T::kKbPerStage, nkb - i);
         for (int j = 0; j < n; ++j)
           tma_load_2d(smem_base + st * T::kStageBytes + T::kStageWBytes + j * T::kXKbBytes, &tmap_x,
@@ -174,7 +176,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
              wait_bounded(bar_sub_done + 8 * ((u + 1) % T::kSubRing), ((u + 1) / T::kSubRing) & 1, ctx, kStProducerEmpty);
         if (!ok) break;
       }
-      if (elect_one()) {
+      if (elect_one() && i != p.fault_skip_kb) {
         SK_TRACE_EVENT(0, issued);
         const uint32_t full = bar_ld_full + 8 * stage;
         const uint32_t dst = smem_base + stage * T::kStageBytes;
@@ -195,7 +197,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       const int first = issued > S ? issued - S : 0;
       for (int i = first; i < issued; ++i) {
         while (!mbar_try_wait(bar_ld_full + 8 * (i % S), (i / S) & 1)) {
-          if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(p.status, 0, kStDrain); break; }
+          if (clock64() - t0 > ctx.limit) { atomicCAS(p.status, 0, kStDrain); break; }
         }
       }
     }

@@ -49,7 +49,7 @@ constexpr int kTileN = 128;          // output features per CTA tile (MMA M)
 constexpr int kBlockK = 128;         // K codes per pipeline stage (= one 128-byte swizzle row of int8)
 constexpr int kWpBytes = kTileN * kBlockK / 4;   // 4096: tiled 2-bit block
 constexpr int kWxBytes = kTileN * kBlockK;       // 16384: expanded int8 block
-constexpr long long kWaitLimitCycles = 1000000000ll;  // every mbarrier wait gives up after 1e9 SM cycles (0.5-0.8 s)
+constexpr long long kWaitLimitCycles = 1000000000ll;  // default: every mbarrier wait gives up after 1e9 SM cycles (0.5-0.8 s)
 constexpr int kScalePrefetchGroups = 8;   // group scales are pulled into L2 this many groups before they are loaded
 constexpr int kBiasFlushGroups = 16;  // the bias term is subtracted from the accumulators this often
 
@@ -97,6 +97,9 @@ struct GemmParams {
   int tma_out;                // 1: the output tile leaves through TMA stores (tensor maps of every destination given)
   int n_tiles;                // ceil(N / 128)
   int num_tiles;              // n_tiles * token tiles
+  long long wait_limit;       // SM cycles after which a wait inside the kernel gives up (kWaitLimitCycles by default)
+  int fault_skip_kb;          // failure-path test hook: the producer leaves out the copies of this K block of its
+                              // range (-1: off), so that the waits for them run into the limit
 #ifdef SK_TRACE
   long long* trace;           // [8][64] clock stamps of CTA (0,0,0)
 #endif
@@ -181,18 +184,20 @@ struct KernelTraits {
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory
   int* status;               // global
+  long long limit;           // SM cycles
 };
 
 // Slow path of a bounded wait (inlined: a real call inside a kernel that re-partitions registers with setmaxnreg
 // does not compile); the fast path in wait_bounded is a single poll.
 // The limit is counted on the SM clock (%globaltimer costs about a microsecond per read).
-__device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long limit) {
   const long long t0 = clock64();
   for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 63u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -203,7 +208,7 @@ __device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatil
 // Bounded wait.  Returns false if the limit expired here or in any other thread of the CTA.
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  return wait_slow(bar, parity, ctx.abort_flag, ctx.status, code);
+  return wait_slow(bar, parity, ctx.abort_flag, ctx.status, code, ctx.limit);
 }
 
 // 16 two-bit codes held in `w` as  sum_{j,b} code[4j+b] << (4b + 2(j&1) + 16(j>>1))  ->  16 int8 bytes
@@ -306,7 +311,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   const uint32_t bar_acc_empty = bar_acc_full + 8u * ACC_BUFS;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::kOffMisc + 4);
-  const WaitCtx ctx{abort_flag, p.status};
+  const WaitCtx ctx{abort_flag, p.status, p.wait_limit};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -382,7 +387,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         for (int kcoord = kb_begin * kBlockK; kcoord < kb_end * kBlockK; kcoord += kBlockK) {
           ok = wait_bounded(empty, phase ^ 1, ctx, kStProducerEmpty);
           if (!ok) break;
-          if (elect_one()) {
+          if (elect_one() && kcoord != (kb_begin + p.fault_skip_kb) * kBlockK) {
             SK_TRACE_EVENT(0, issued);
             mbar_arrive_expect_tx(full, kStageTxBytes);
             bulk_load_1d(dst_wp, wsrc, kWpBytes, full);
@@ -407,7 +412,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           const int l = i % LSTAGES;
           const uint32_t ph = (i / LSTAGES) & 1;
           while (!mbar_try_wait(bar_ld_full + 8 * l, ph)) {
-            if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(p.status, 0, kStDrain); break; }
+            if (clock64() - t0 > ctx.limit) { atomicCAS(p.status, 0, kStDrain); break; }
           }
         }
       }
@@ -481,12 +486,6 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             SK_TRACE_EVENT(2, SK_TRACE_BASE + kb - kb_begin);
           }
           __syncwarp();
-#ifdef SK_TRACE_MMA_LATENCY
-          if (kb - kb_begin >= 8 && kb - kb_begin < 24) {   // diagnostic: how long do the 4 MMAs take to complete?
-            while (!mbar_try_wait(bar_acc_full + 8 * ab, aph)) {}
-            if (lane == 0) SK_TRACE_EVENT(5, kb - kb_begin);
-          }
-#endif
           if (++l == LSTAGES) { l = 0; lph ^= 1; }
           if (++e == ESTAGES) { e = 0; eph ^= 1; }
           if (++ab == ACC_BUFS) { ab = 0; aph ^= 1; }

@@ -45,7 +45,7 @@ class W2A8Linear(nn.Module):
         self.register_buffer("w_scale", w_scale, persistent=True)
         self.group_size, self.zero_point, self.out_dtype = group_size, zero_point, out_dtype
         self.out_features, self.in_features = w_packed.shape[0], w_packed.shape[1] * 4
-        self._plan = None
+        self._plan, self._plan_key = None, None
 
     @classmethod
     def from_float(cls, weight_out_in, group_size=128, device="cuda", out_dtype=torch.float16):
@@ -55,9 +55,14 @@ class W2A8Linear(nn.Module):
         return cls(w_packed, w_scale, group_size, 1, out_dtype)
 
     def plan(self) -> W2A8Plan:
-        if self._plan is None:
+        """The plan of the CURRENT weight buffers: it holds a tiled copy of w_packed and a pointer to w_scale, so it
+        is rebuilt when the buffers were written in place (load_state_dict) or replaced (.to(), .cuda())."""
+        key = (self.w_packed.data_ptr(), self.w_packed._version, self.w_scale.data_ptr(), self.w_scale._version,
+               self.w_packed.device)
+        if self._plan is None or self._plan_key != key:
             self._plan = W2A8Plan(self.w_packed, self.w_scale, group_size=self.group_size, zero_point=self.zero_point,
                                   out_dtype=self.out_dtype)
+            self._plan_key = key
         return self._plan
 
     def forward_quantized(self, x_q, x_scale):

@@ -111,6 +111,12 @@ class W2A8Plan:
     def device_status(self) -> int:
         return torch.ops.slimkernels.w2a8_plan_device_status(self._h)
 
+    def query_launch(self, M: int) -> dict:
+        """The launch the plan makes for M tokens: token tile, split-K factor, CTAs and kernel kind
+        (1 general tcgen05 kernel, 2 CUDA-core checker, 3 decode tcgen05 kernel)."""
+        t, s, c, k = torch.ops.slimkernels.w2a8_plan_query_launch(self._h, int(M))
+        return {"token_tile": t, "split_k": s, "ctas": c, "kernel": k}
+
 
 def _destroy(handle):
     try:
@@ -119,36 +125,23 @@ def _destroy(handle):
         pass
 
 
-# plans of the functional op, keyed by the identity of the weight tensor and dropped with it
-_plan_cache: dict = {}
-
-
-def _cached_plan(w_packed, w_scale, group_size, zero_point, out_dtype) -> W2A8Plan:
-    key = (id(w_packed), id(w_scale), group_size, zero_point, out_dtype)
-    ent = _plan_cache.get(key)
-    ver = (w_packed._version, w_scale._version, w_packed.data_ptr(), w_scale.data_ptr())
-    if ent is not None and ent[0] == ver:
-        return ent[1]
-    plan = W2A8Plan(w_packed, w_scale, group_size=group_size, zero_point=zero_point, out_dtype=out_dtype)
-    _plan_cache[key] = (ver, plan)
-    weakref.finalize(w_packed, _plan_cache.pop, key, None)
-    return plan
-
-
 def w2a8_gemm(x_q, x_scale, w_packed, w_scale, group_size: int = 128, zero_point: int = 1,
               out_dtype=torch.float16):
     """out[M, N] = x_scale[:, None] * sum_g w_scale[g] * (x_q[:, g] @ (codes[:, g] - zero_point).T).
 
     x_q int8 [M, K], x_scale float32 [M], w_packed uint8 [N, K/4] (first code of a byte in bits 7:6),
-    w_scale float16 [K/group_size, N].  The plan (tiled weight copy) is built on first use of a weight
-    tensor and reused while that tensor object is alive and unmodified.
+    w_scale float16 [K/group_size, N].  This is the registered op ``torch.ops.slimkernels.w2a8_gemm``: the plan
+    (tiled weight copy) is built on first use of a weight tensor and kept, weakly, while that tensor object is
+    alive and unmodified (it is rebuilt after an in-place write and dropped with the tensor).
     """
-    return _cached_plan(w_packed, w_scale, group_size, zero_point, out_dtype).gemm(x_q, x_scale)
+    load_extension()
+    return torch.ops.slimkernels.w2a8_gemm(x_q, x_scale, w_packed, w_scale, group_size, zero_point, out_dtype)
 
 
 def w2a8_partials(x_q, w_packed, w_scale, group_size: int = 128, zero_point: int = 1):
     """int32 [K/G, M, N]: the exact per-group integer partial sums the GEMM scales and adds."""
-    return _cached_plan(w_packed, w_scale, group_size, zero_point, torch.float16).partials(x_q)
+    load_extension()
+    return torch.ops.slimkernels.w2a8_partials(x_q, w_packed, w_scale, group_size, zero_point)
 
 
 def repack_weight(w_packed):

@@ -6,17 +6,51 @@ N-sharding:
 
 Output features are independent, so rank r owns rows [r*N/R, (r+1)*N/R) of w_packed and the matching
 columns of w_scale; activations are replicated; K is not split, so no reduction is needed.  The only
-exchange is an all-gather of the fp16/bf16 output over NVLink (NCCL through torch.distributed).
+exchange is an all-gather of the fp16/bf16 output over NVLink: either NCCL after the GEMM, or (fused=True) the
+GEMM's epilogue stores every finished tile into every rank's output buffer through peer pointers.
 The reference has no multi-GPU code; this is the one parallel strategy the W2A8 path needs.
+
+Failure behaviour.  The reference aborts the process on any CUDA error
+(slimkernels/cute/gemm/wgmma_sm90_W2A8.cu:489-505); here a rank that is late or gone surfaces as a Python
+exception (ExchangeTimeout) on the ranks that are still alive, raised on the HOST before the next launch:
+  * every blocking collective on CPU tensors is issued asynchronously and waited for with a limit;
+  * with a `control_group` (a gloo group over the same ranks) every step starts with a monitored barrier on
+    the host, so a missing rank is noticed before a kernel that would wait for it is launched.
+Nothing here makes a GPU wait without a limit, and no test hangs or faults a GPU.
 """
 from __future__ import annotations
 
+import datetime
 import os
 
 import torch
 import torch.distributed as dist
 
 from .ops import W2A8Plan
+
+
+class ExchangeTimeout(RuntimeError):
+    """A rank did not take part in an exchange within the limit.  Carries rank, step and what was waited for."""
+
+    def __init__(self, rank: int, step: int, what: str, limit_s: float, detail: str = ""):
+        self.rank, self.step, self.what, self.limit_s = rank, step, what, limit_s
+        super().__init__(f"rank {rank}, step {step}: {what} did not complete within {limit_s:.3g} s"
+                         + (f" ({detail})" if detail else ""))
+
+
+def _wait_with_limit(work, rank: int, step: int, what: str, limit_s):
+    """Waits for an asynchronous collective.  CPU (gloo) work honours the limit and raises ExchangeTimeout;
+    CUDA (NCCL) work is stream-ordered, so wait() only orders the stream and the limit is enforced by the process
+    group's own timeout (init_process_group(timeout=...)) and, where given, by the control group."""
+    if work is None:
+        return
+    try:
+        if limit_s is None:
+            work.wait()
+        else:
+            work.wait(datetime.timedelta(seconds=float(limit_s)))
+    except RuntimeError as exc:      # gloo reports expiry (and peers that closed their connection) this way
+        raise ExchangeTimeout(rank, step, what, float(limit_s or 0.0), str(exc).splitlines()[0]) from exc
 
 
 def shard_bounds(N: int, world: int, rank: int, multiple: int = 128):
@@ -33,11 +67,36 @@ def shard_weight(w_packed, w_scale, world: int, rank: int):
     return w_packed[lo:hi].contiguous(), w_scale[:, lo:hi].contiguous()
 
 
+class _Liveness:
+    """Host-side check that every rank is still taking part, made before a step is launched."""
+
+    def __init__(self, control_group, limit_s, rank):
+        self.group, self.limit_s, self.rank = control_group, limit_s, rank
+
+    def check(self, step: int):
+        if self.group is None or self.limit_s is None:
+            return
+        try:
+            dist.monitored_barrier(self.group, timeout=datetime.timedelta(seconds=float(self.limit_s)))
+        except RuntimeError as exc:
+            raise ExchangeTimeout(self.rank, step, "liveness barrier before the launch", float(self.limit_s),
+                                  str(exc).splitlines()[0]) from exc
+
+
 class ShardedW2A8Gemm:
-    """Holds this rank's weight slice; ``forward`` returns the full [M, N] output on every rank."""
+    """Holds this rank's weight slice; ``forward`` returns the full [M, N] output on every rank.
+
+    The returned tensor is a buffer owned by the op and is reused: it stays valid until the SECOND next call with
+    the same M (two buffers alternate), so a consumer may still read step i's result while step i+1 runs, also on
+    another stream, but must be ordered before step i+2 is launched.
+
+    exchange_timeout_s: limit for the host-side waits (CPU collectives, liveness barrier); None = no limit.
+    control_group: optional gloo group over the same ranks for the liveness barrier that precedes every launch.
+    """
 
     def __init__(self, w_packed_local, w_scale_local, N_total: int, group=None, group_size=128, zero_point=1,
-                 out_dtype=torch.float16, plan_factory=W2A8Plan, fused=False):
+                 out_dtype=torch.float16, plan_factory=W2A8Plan, fused=False, exchange_timeout_s=None,
+                 control_group=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -49,55 +108,79 @@ class ShardedW2A8Gemm:
         # stand-in for the device GEMM; the product default is the CUDA plan and nothing else
         self.plan = plan_factory(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
                                  out_dtype=out_dtype)
-        self._bufs = {}
         self.fused = bool(fused) and self.world > 1
-        self._symm = {}
+        self.timeout_s = exchange_timeout_s
+        self._live = _Liveness(control_group, exchange_timeout_s, self.rank)
+        self._local = {}       # (M, device) -> [M, N_local]
+        self._gather = {}      # (M, device) -> ([R, M, N_local], [[M, N_total]] x 2)
+        self._symm = {}        # (M, device) -> [(buffer, handle, peer pointers)] x 2
+        self._step = 0
 
-    def _buffers(self, M, device):
+    # ---- buffers (made on first use of a token count, then kept; only what the chosen exchange needs)
+    def _local_buffer(self, M, device):
         key = (M, device)
-        if key not in self._bufs:
-            local = torch.empty(M, self.N_local, dtype=self.out_dtype, device=device)
-            gathered = torch.empty(self.world, M, self.N_local, dtype=self.out_dtype, device=device)
-            full = torch.empty(M, self.N_total, dtype=self.out_dtype, device=device)
-            self._bufs[key] = (local, gathered, full)
-        return self._bufs[key]
+        if key not in self._local:
+            self._local[key] = torch.empty(M, self.N_local, dtype=self.out_dtype, device=device)
+        return self._local[key]
 
-    def local_gemm(self, x_q, x_scale):
-        local, _, _ = self._buffers(x_q.shape[0], x_q.device)
-        return self.plan.gemm(x_q, x_scale, out=local)
+    def _gather_buffers(self, M, device):
+        key = (M, device)
+        if key not in self._gather:
+            gathered = torch.empty(self.world, M, self.N_local, dtype=self.out_dtype, device=device)
+            full = [torch.empty(M, self.N_total, dtype=self.out_dtype, device=device) for _ in range(2)]
+            self._gather[key] = (gathered, full)
+        return self._gather[key]
 
     def _symmetric(self, M, device):
-        """[M, N_total] output buffer in symmetric memory + the peers' pointers to it (this rank's first, then the
-        others in ring order so that the ranks do not all write to the same peer at the same time)."""
+        """Two [M, N_total] output buffers in symmetric memory, each with the peers' pointers to it (this rank's
+        first, then the others in ring order so that the ranks do not all write to the same peer at the same time)."""
         key = (M, device)
         if key not in self._symm:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
             import torch.distributed._symmetric_memory as symm_mem
             group = self.group if self.group is not None else dist.group.WORLD
-            buf = symm_mem.empty((M, self.N_total), dtype=self.out_dtype, device=device)
-            hdl = symm_mem.rendezvous(buf, group)
-            ptrs = [int(hdl.buffer_ptrs[(self.rank + i) % self.world]) for i in range(self.world)]
-            self._symm[key] = (buf, hdl, ptrs)
+            slots = []
+            for _ in range(2):
+                buf = symm_mem.empty((M, self.N_total), dtype=self.out_dtype, device=device)
+                hdl = symm_mem.rendezvous(buf, group)
+                ptrs = [int(hdl.buffer_ptrs[(self.rank + i) % self.world]) for i in range(self.world)]
+                slots.append((buf, hdl, ptrs))
+            self._symm[key] = slots
         return self._symm[key]
 
+    def local_gemm(self, x_q, x_scale):
+        """This rank's GEMM alone (no exchange): [M, N_local]."""
+        return self.plan.gemm(x_q, x_scale, out=self._local_buffer(x_q.shape[0], x_q.device))
+
     def forward_fused(self, x_q, x_scale):
+        """GEMM whose epilogue stores every tile into all ranks' buffers, then one stream-ordered device barrier.
+        Two buffers alternate: a rank that is a step ahead writes into the buffer its peers are NOT reading (a
+        rank passes the barrier of step i+1 only after every rank's stream has reached it, i.e. after every
+        rank's same-stream consumers of step i are done), so step i+2 may overwrite step i's buffer."""
         M = x_q.shape[0]
-        buf, hdl, ptrs = self._symmetric(M, x_q.device)
+        self._live.check(self._step)
+        buf, hdl, ptrs = self._symmetric(M, x_q.device)[self._step & 1]
         self.plan.gemm_scatter(x_q, x_scale, ptrs, self.N_total, self.rank * self.N_local)
-        hdl.barrier()          # every rank's tiles have landed everywhere (stream-ordered device barrier)
+        hdl.barrier()          # every rank's tiles have landed everywhere
+        self._step += 1
         return buf
 
     def forward(self, x_q, x_scale):
         if self.fused:
             return self.forward_fused(x_q, x_scale)
         M = x_q.shape[0]
-        local, gathered, full = self._buffers(M, x_q.device)
-        self.plan.gemm(x_q, x_scale, out=local)
+        local = self.local_gemm(x_q, x_scale)
         if self.world == 1:
             return local
-        dist.all_gather_into_tensor(gathered.view(self.world * M, self.N_local), local, group=self.group)
+        self._live.check(self._step)
+        gathered, fulls = self._gather_buffers(M, x_q.device)
+        full = fulls[self._step & 1]
+        work = dist.all_gather_into_tensor(gathered.view(self.world * M, self.N_local), local, group=self.group,
+                                           async_op=True)
+        _wait_with_limit(work, self.rank, self._step, "all-gather of the output", self.timeout_s)
         # [R, M, N/R] -> [M, R, N/R] == [M, N]
         full.view(M, self.world, self.N_local).copy_(gathered.permute(1, 0, 2))
+        self._step += 1
         return full
 
     __call__ = forward
@@ -124,7 +207,7 @@ class KShardedW2A8Gemm:
     """
 
     def __init__(self, w_packed_local, w_scale_local, group=None, group_size=128, zero_point=1,
-                 out_dtype=torch.float16, plan_factory=W2A8Plan):
+                 out_dtype=torch.float16, plan_factory=W2A8Plan, exchange_timeout_s=None, control_group=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -132,6 +215,9 @@ class KShardedW2A8Gemm:
         self.out_dtype = out_dtype
         self.plan = plan_factory(w_packed_local, w_scale_local, group_size=group_size, zero_point=zero_point,
                                  out_dtype=out_dtype)
+        self.timeout_s = exchange_timeout_s
+        self._live = _Liveness(control_group, exchange_timeout_s, self.rank)
+        self._step = 0
 
     def forward(self, x_q_local, x_scale_local):
         M = x_q_local.shape[0]
@@ -140,9 +226,12 @@ class KShardedW2A8Gemm:
             return partial
         if M % self.world != 0:
             raise ValueError(f"M={M} must be a multiple of the world size {self.world}")
+        self._live.check(self._step)
         rows = M // self.world
         recv = torch.empty_like(partial)                                     # [R, M/R, N]: block j from rank j
-        dist.all_to_all_single(recv, partial.contiguous(), group=self.group)
+        work = dist.all_to_all_single(recv, partial.contiguous(), group=self.group, async_op=True)
+        _wait_with_limit(work, self.rank, self._step, "exchange of the partial sums", self.timeout_s)
+        self._step += 1
         return recv.view(self.world, rows, self.N).float().sum(dim=0).to(self.out_dtype)
 
     def forward_full(self, x_q_local, x_scale_local):
@@ -150,7 +239,8 @@ class KShardedW2A8Gemm:
         if self.world == 1:
             return mine
         full = torch.empty(self.world * mine.shape[0], self.N, dtype=self.out_dtype, device=mine.device)
-        dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
+        work = dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group, async_op=True)
+        _wait_with_limit(work, self.rank, self._step, "all-gather of the reduced rows", self.timeout_s)
         return full
 
     __call__ = forward

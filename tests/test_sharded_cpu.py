@@ -129,3 +129,79 @@ def test_shard_bounds_rejects_ragged_split():
         shard_bounds(4096 + 128, 8, 0)
     assert shard_bounds(57344, 8, 7) == (50176, 57344)
     assert shard_bounds(8192, 8, 3) == (3072, 4096)
+
+
+# --------------------------------------------------------------------------------------------------
+# Failure behaviour, made on the host: a rank that arrives late, and a rank that never takes part.
+# --------------------------------------------------------------------------------------------------
+def _worker_fail(rank, world, port, q, mode):
+    """mode 'late': rank 1 joins the exchange 1 s late (inside the limit).  mode 'missing': rank 1 never calls the
+    op.  mode 'liveness': as 'missing', noticed by the control group's barrier before anything is launched."""
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from slimkernels_b200 import workloads as W
+    from slimkernels_b200.torch.sharded import ExchangeTimeout, ShardedW2A8Gemm, shard_weight
+    M, N, K, G = 6, 512, 256, 128
+    x_q, x_scale, w_packed, w_scale = W.make_problem(M, N, K, G, seed=0)
+    wl, sl = shard_weight(torch.from_numpy(w_packed), torch.from_numpy(w_scale), world, rank)
+    limit = 20.0 if mode == "late" else 1.5
+    control = dist.new_group(backend="gloo") if mode == "liveness" else None
+    op = ShardedW2A8Gemm(wl, sl, N, group_size=G, plan_factory=OraclePlan, exchange_timeout_s=limit,
+                         control_group=control)
+    xq, xs = torch.from_numpy(x_q), torch.from_numpy(x_scale)
+    out = None
+    if mode == "late":
+        if rank == 1:
+            time.sleep(1.0)
+        y = op(xq, xs)
+        out = (rank, "ok", tuple(y.shape), 0.0)
+    elif rank == 1:
+        time.sleep(6.0)                       # alive on the host, but never joins the exchange
+        out = (rank, "absent", (), 0.0)
+    else:
+        t0 = time.perf_counter()
+        try:
+            op(xq, xs)
+            out = (rank, "no error", (), time.perf_counter() - t0)
+        except ExchangeTimeout as exc:
+            ok = exc.rank == 0 and exc.step == 0 and exc.limit_s == limit and "step 0" in str(exc)
+            out = (rank, "timeout" if ok else f"bad exception fields: {exc}", (exc.what,), time.perf_counter() - t0)
+    q.put(out)
+    q.close()
+    q.join_thread()
+    os._exit(0)      # the group is unusable after an expired wait: leave without the collective teardown
+
+
+def _run_fail(mode):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_fail, args=(r, world, port, q, mode)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict((r[0], r) for r in (q.get(timeout=90) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=60)
+    return results
+
+
+def test_late_rank_still_completes_inside_the_limit():
+    res = _run_fail("late")
+    assert res[0][1] == "ok" and res[1][1] == "ok" and res[0][2] == (6, 512)
+
+
+def test_missing_rank_surfaces_as_exchange_timeout():
+    res = _run_fail("missing")
+    assert res[0][1] == "timeout", res[0]
+    assert "all-gather" in res[0][2][0]
+    assert 1.0 <= res[0][3] < 5.5, f"the error took {res[0][3]:.1f} s to surface (limit 1.5 s)"
+
+
+def test_missing_rank_is_noticed_by_the_liveness_barrier_before_the_launch():
+    res = _run_fail("liveness")
+    assert res[0][1] == "timeout", res[0]
+    assert "liveness" in res[0][2][0]
+    assert res[0][3] < 5.5

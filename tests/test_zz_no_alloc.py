@@ -57,14 +57,20 @@ def test_static_mlp_matches_workspace_mlp_twice_in_a_row(built_libs):
                       torch.zeros(M, hidden, dtype=torch.float16, device=dev)))
     torch.cuda.synchronize(dev)
 
-    for M, x, ws, out_ref, out_static in cases:
+    for M, x, ws, out_ref, out_static in cases:           # the reference results first: this also loads every kernel
         rc = lib.sk_w2a8_mlp_forward(gu.handle, dn.handle, M, x.data_ptr(), hidden, out_ref.data_ptr(), hidden,
                                      ws.data_ptr(), ws.numel(), stream)
         assert rc == capi.SK_OK
+    torch.cuda.synchronize(dev)
+    free = []
+    for M, x, ws, out_ref, out_static in cases:
         rc = lib.sk_w2a8_mlp_forward_static(gu.handle, dn.handle, M, x.data_ptr(), hidden, out_static.data_ptr(),
                                             hidden, stream)
         assert rc == capi.SK_OK, capi.status_string(rc)
-    torch.cuda.synchronize(dev)
+        torch.cuda.synchronize(dev)
+        free.append(torch.cuda.mem_get_info(dev)[0])
+    # the first call looked the array's address up; the second call must not take any device memory
+    assert free[1] >= free[0], "the allocation-free entry point consumed device memory"
     assert gu.device_status() == 0 and dn.device_status() == 0
     for M, x, ws, out_ref, out_static in cases:
         assert torch.isfinite(out_ref).all() and out_ref.abs().max() > 0
