@@ -242,13 +242,33 @@ def decode_sweep(dev, peaks):
                 ms_graph = time_events(g.replay, 10, st) / calls
                 # single launches of one plan, back to back (L2-warm, launch-bound): reported for context
                 ms_single = time_events(lambda: plans[0].gemm(x_q, xs, out=outs[0]), 50, st)
+                # the floor of this launch geometry: the same chain with an empty kernel (same grid, cluster, block,
+                # shared memory, dependent launch; barrier set-up, tensor-memory allocation, the barriers; no bytes)
+                for i in range(4):
+                    plans[i % ncopies].launch_floor_probe(M)
+                st.synchronize()
+                gf = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gf, stream=st):
+                    for i in range(calls):
+                        plans[i % ncopies].launch_floor_probe(M)
+                for _ in range(3):
+                    gf.replay()
+                st.synchronize()
+                ms_floor = time_events(gf.replay, 10, st) / calls
             us = ms_graph * 1e3
+            us_floor = ms_floor * 1e3
             gbs = wbytes / (ms_graph * 1e-3) / 1e9
+            stream_us = wbytes / (peaks["hbm_gbs"] * 1e9) * 1e6
+            q = plans[0].query_launch(M)
             out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(us, 3), "gbs": round(gbs, 1),
                         "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "us_single_launch_l2_warm": round(ms_single * 1e3, 3),
+                        "us_launch_floor": round(us_floor, 3),
+                        "us_streaming_at_peak": round(stream_us, 3),
+                        "gbs_above_floor": round(wbytes / max(us - us_floor, 1e-3) / 1e3, 1),
+                        "frac_hbm_ceiling_floor_plus_streaming": round(stream_us / (us_floor + stream_us), 4),
                         "weight_copies": ncopies, "algorithmic_bytes": wbytes,
-                        "kernel": "w2a8_decode_kernel<%d> (tcgen05.mma kind::i8, weights expanded into tensor memory)"
-                                  % (16 if M <= 16 else 32)})
+                        "kernel": "w2a8_decode_kernel (tcgen05.mma kind::i8, weights expanded into tensor memory): "
+                                  f"token tile {q['token_tile']}, split-K {q['split_k']}, {q['ctas']} CTAs"})
         del plans
         torch.cuda.empty_cache()
     return out

@@ -179,6 +179,12 @@ int sk_w2a8_last_cuda_error(const sk_w2a8_plan* plan);
 /* Describes the launch the plan would make for M tokens: token tile, split-K factor, CTAs, kernel kind. */
 int sk_w2a8_query_launch(sk_w2a8_plan* plan, int64_t M, int* token_tile, int* split_k, int* ctas,
                          int* kernel_kind);
+/* Measurement aid (decode-sized M only, else SK_ERR_UNAVAILABLE): launches an EMPTY kernel with the grid, cluster,
+ * block size, shared memory and launch attributes sk_w2a8_gemm would use for M tokens, doing only the fixed per-CTA
+ * work (barrier set-up, tensor-memory allocation and release, the barriers).  Timed as a chain in a CUDA graph it gives
+ * the per-launch floor of this launch geometry, against which the GEMM's time is to be read.  No counterpart in the
+ * reference. */
+int sk_w2a8_launch_floor_probe(sk_w2a8_plan* plan, int64_t M, sk_stream_t stream);
 const char* sk_status_string(int status);
 int sk_w2a8_version(void);
 

@@ -55,6 +55,7 @@ SIGNATURES = {
     "sk_device_status_string": (ctypes.c_char_p, [_int]),
     "sk_w2a8_query_launch": (_int, [_vp, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(_int),
                                     ctypes.POINTER(_int)]),
+    "sk_w2a8_launch_floor_probe": (_int, [_vp, _i64, _vp]),
     "sk_status_string": (ctypes.c_char_p, [_int]),
     "sk_w2a8_version": (_int, []),
 }

@@ -127,6 +127,40 @@ __global__ void w2a8_simt_kernel(const int8_t* __restrict__ x_q, long long ld_x,
 }
 
 // ------------------------------------------------------------------------------------------------
+// Launch-floor probe: what a decode-sized launch costs before it moves a byte.  Same grid, cluster, block size,
+// dynamic shared memory and launch attributes as the decode kernel would use, and the same fixed work per CTA
+// (barrier initialisation, tensor-memory allocation, one CTA barrier, the cluster barrier of the split-K reduction,
+// release); no copies, no arithmetic.  A chain of these in a CUDA graph gives the time per launch below which no
+// kernel of this geometry can go.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(DecodeTraits<16>::kThreads, 2) launch_floor_kernel(int* sink) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) unsigned long long bars[16];
+  grid_dep_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 16; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    fence_mbar_init();
+  }
+  if (threadIdx.x / 32 == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 256);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  grid_dep_wait();
+  if (gridDim.z > 1) cluster_sync_all();
+  if (sink && smem_raw[threadIdx.x] == 0xff && tmem_slot == 0xffffffffu) *sink = 1;   // keeps the dynamic allocation referenced
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x / 32 == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc(tmem_slot, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -287,12 +321,9 @@ static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmP
     ++na;
   }
   // Programmatic dependent launch: this kernel's set-up and first weight copies may overlap the tail of the previous
-  // kernel in the stream (the kernel itself waits for that kernel before it touches activations or outputs).
-  // Measured: it pays when the grid does not fit one CTA per SM (the early CTAs fill SMs the previous kernel's last
-  // wave leaves idle: -8..-17 %), and costs when it does (the early CTAs only poll next to the running ones:
-  // +8..+25 %), so by default it is used for the former only.
-  const long long ctas = static_cast<long long>(plan->n_tiles) * m_tiles * split_k;
-  if (!DUMP && (plan->opt_pdl == 2 || (plan->opt_pdl == 0 && ctas > plan->sm_count))) {
+  // kernel in the stream (the kernel itself waits for that kernel before it touches activations or outputs, and its
+  // roles sit in griddepcontrol.wait rather than poll).  SK_OPT_DEPENDENT_LAUNCH = 1 launches plainly.
+  if (!DUMP && plan->opt_pdl != 1) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
@@ -787,6 +818,52 @@ int sk_w2a8_last_device_status(sk_w2a8_plan* plan, int* device_status) {
 }
 
 int sk_w2a8_last_cuda_error(const sk_w2a8_plan* plan) { return plan ? plan->last_cuda_error : 0; }
+
+int sk_w2a8_launch_floor_probe(sk_w2a8_plan* plan, int64_t M, sk_stream_t stream) {
+  if (!plan) return SK_ERR_NULL_POINTER;
+  if (M <= 0) return SK_ERR_BAD_SHAPE;
+  sk::LaunchChoice ch;
+  int rc = sk::resolve_launch(plan, M, false, &ch);
+  if (rc != SK_OK) return rc;
+  if (ch.kernel != 3) return SK_ERR_UNAVAILABLE;   // the probe mirrors the decode kernel's launch
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) return sk::cuda_fail(plan, cudaGetLastError());
+  if (cur != plan->device && cudaSetDevice(plan->device) != cudaSuccess) return sk::cuda_fail(plan, cudaGetLastError());
+  const int dyn = ch.token_tile == 16 ? sk::DecodeTraits<16>::kDynamicBytes : sk::DecodeTraits<32>::kDynamicBytes;
+  static int configured[64] = {0};
+  cudaError_t e = cudaSuccess;
+  if (plan->device < 64 && !configured[plan->device]) {
+    e = cudaFuncSetAttribute(sk::launch_floor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    configured[plan->device] = 1;
+  }
+  if (e == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    const int m_tiles = static_cast<int>((M + ch.token_tile - 1) / ch.token_tile);
+    cfg.gridDim = dim3(plan->n_tiles, m_tiles, ch.split_k);
+    cfg.blockDim = dim3(sk::DecodeTraits<16>::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = dyn - 1024;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (ch.split_k > 1) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 1;
+      attr[na].val.clusterDim.y = 1;
+      attr[na].val.clusterDim.z = ch.split_k;
+      ++na;
+    }
+    if (plan->opt_pdl != 1) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    e = cudaLaunchKernelEx(&cfg, sk::launch_floor_kernel, static_cast<int*>(nullptr));
+  }
+  if (cur != plan->device) (void)cudaSetDevice(cur);
+  return e == cudaSuccess ? SK_OK : sk::cuda_fail(plan, e);
+}
 
 const char* sk_device_status_string(int device_status) {
   switch (device_status) {

@@ -184,6 +184,11 @@ std::vector<int64_t> query_launch(int64_t handle, int64_t M) {
   return {t, sp, c, k};
 }
 
+void launch_floor_probe(int64_t handle, const at::Tensor& on_device_of, int64_t M) {
+  c10::cuda::CUDAGuard guard(on_device_of.device());
+  check(sk_w2a8_launch_floor_probe(as_plan(handle), M, at::cuda::getCurrentCUDAStream().stream()), "w2a8_launch_floor_probe");
+}
+
 int64_t device_status(int64_t handle) {
   int v = 0;
   int rc = sk_w2a8_last_device_status(as_plan(handle), &v);
@@ -304,6 +309,7 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
   m.def("w2a8_plan_query_launch(int plan, int M) -> int[]", &query_launch);
+  m.def("w2a8_plan_launch_floor_probe(int plan, Tensor on_device_of, int M) -> ()", &launch_floor_probe);
   m.def("quantize_activation_int8(Tensor x) -> (Tensor, Tensor)", &quantize_activation);
   m.def("w2a8_quantize_weight(Tensor w_kn, int group_size) -> (Tensor, Tensor, Tensor)", &quantize_weight);
   m.def("silu_mul_quantize_int8(Tensor gate_up) -> (Tensor, Tensor)", &silu_mul_quantize);

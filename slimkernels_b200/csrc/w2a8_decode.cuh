@@ -34,6 +34,24 @@
 
 namespace sk {
 
+// Bounded wait for a role that is not on the critical path of a K block: sleeps between polls, so that it does not
+// take issue slots and integer-pipe cycles from the warps that expand (the expansion saturates the integer pipe).
+__device__ __forceinline__ bool wait_bounded_relaxed(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code,
+                                                     unsigned sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*ctx.abort_flag) return false;
+    if (clock64() - t0 > ctx.limit) {
+      *ctx.abort_flag = 1;
+      atomicCAS(ctx.status, 0, code);
+      return false;
+    }
+  }
+}
+
 template <int TOK>
 struct DecodeTraits {
   static_assert(TOK == 16 || TOK == 32, "token tile of the decode kernel");
@@ -108,15 +126,33 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 
   // ---------------------------------------------------------------- set-up
   if (threadIdx.x == 0) SK_TRACE_EVENT(4, 0);
-  if (threadIdx.x == 0) {
+  // Programmatic dependent launch: the next kernel in the stream may be scheduled as soon as every CTA of this one
+  // got here, and this kernel may itself have started before the previous one finished.  Weights and group scales
+  // are constants, so the copies of the first stages' weights go out at once -- from the thread that initialises the
+  // barriers, before tensor memory is allocated and before the CTA's first barrier --; every thread that reads
+  // activations or token scales or writes outputs waits for the previous kernel first (grid_dep_wait below).
+  grid_dep_launch_dependents();
+  if (warp == kProducerWarp && lane == 0) {
     for (int i = 0; i < S; ++i) mbar_init(bar_ld_full + 8 * i, 1);
+    fence_mbar_init();
+    const uint8_t* w = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
+    for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
+      const int n = min(T::kKbPerStage, nkb - i);
+      if (i != p.fault_skip_kb) {   // (failure-path test hook: this stage is never filled)
+        const uint32_t full = bar_ld_full + 8 * st;
+        SK_TRACE_EVENT(0, st);
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(n) * (kWpBytes + T::kXKbBytes));
+        bulk_load_1d(smem_base + st * T::kStageBytes, w, static_cast<uint32_t>(n) * kWpBytes, full);
+      }
+      w += static_cast<size_t>(n) * kWpBytes;
+    }
     for (int i = 0; i < T::kSubRing; ++i) mbar_init(bar_sub_done + 8 * i, 1);
     for (int i = 0; i < T::kASubs; ++i) mbar_init(bar_ex_full + 8 * i, T::kExpWarps);
     for (int i = 0; i < 2; ++i) mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
+    prefetch_tensormap(&tmap_x);
   }
-  if (warp == kProducerWarp && lane == 0) prefetch_tensormap(&tmap_x);
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), T::kTmemCols);
     tmem_relinquish();
@@ -126,32 +162,13 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) SK_TRACE_EVENT(4, 1);
-  // Programmatic dependent launch: the next kernel in the stream may be scheduled as soon as this CTA gets here, and
-  // this kernel may itself have started before the previous one finished.  Weights and group scales are constants,
-  // so the copies of the first stages' weights go out at once; every thread that reads activations or token scales
-  // or writes outputs waits for the previous kernel first (grid_dep_wait below).
-  grid_dep_launch_dependents();
-
   if (warp == kProducerWarp) {
     // ============================================================ producer (whole warp loops, one lane issues)
     const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
     int stage = 0, issued = 0;
     bool ok = true;
-    // first round of stages: the weight copies first (they depend on nothing), then, once the previous kernel in the
-    // stream is complete, the activation boxes
-    if (elect_one()) {
-      const uint8_t* w = wsrc;
-      for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
-        if (i == p.fault_skip_kb) continue;   // failure-path test hook: this stage is never filled
-        const int n = min(T::kKbPerStage, nkb - i);
-        const uint32_t full = bar_ld_full + 8 * st;
-        SK_TRACE_EVENT(0, st);
-        mbar_arrive_expect_tx(full, static_cast<uint32_t>(n) * (kWpBytes + T::kXKbBytes));
-        bulk_load_1d(smem_base + st * T::kStageBytes, w, static_cast<uint32_t>(n) * kWpBytes, full);
-        w += static_cast<size_t>(n) * kWpBytes;
-      }
-    }
-    __syncwarp();
+    // first round of stages: the weight copies are under way already (set-up); once the previous kernel in the stream
+    // is complete, the activation boxes
     grid_dep_wait();
     if (elect_one()) {
       for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
@@ -172,8 +189,8 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       const int n = min(T::kKbPerStage, nkb - i);
       {   // both half stages of the stage's previous use (they are committed by different warps, in any order)
         const int u = 2 * (issued - S);
-        ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStProducerEmpty) &&
-             wait_bounded(bar_sub_done + 8 * ((u + 1) % T::kSubRing), ((u + 1) / T::kSubRing) & 1, ctx, kStProducerEmpty);
+        ok = wait_bounded_relaxed(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStProducerEmpty, 200) &&
+             wait_bounded_relaxed(bar_sub_done + 8 * ((u + 1) % T::kSubRing), ((u + 1) / T::kSubRing) & 1, ctx, kStProducerEmpty, 200);
         if (!ok) break;
       }
       if (elect_one() && i != p.fault_skip_kb) {
@@ -213,6 +230,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     const int mma_id = warp - kMmaWarp;
     bool ok = true;
     const int num_subs = (nkb + 1) >> 1;
+    grid_dep_wait();   // the MMAs read activations: sit here (no issue slots) rather than poll next to the running kernel
     for (int u = mma_id; u < num_subs; u += 2) {   // one half stage: two K blocks, eight MMAs, one accumulator set
       const int i0 = 2 * u;
       const int q = u >> 1;                     // load stage counter
@@ -252,6 +270,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     int stage = 0, a = 0;
     uint32_t lph = 0;
     bool ok = true;
+    grid_dep_wait();   // a stage is complete only with its activations: do not poll next to the running kernel
     for (int i = 0; i < nkb && ok; i += 2) {
       if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(6, (i >> 1) * 8 + 0);
       // The loads below must not be issued before the waits have been seen to succeed: a load that does not depend
@@ -335,6 +354,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
     float c_cur[GS], c_next[GS];
     coeffs(0, c_cur);
+    grid_dep_wait();   // nothing completes before the activations exist: do not poll next to the running kernel
     float s_sum = 0.f;
     int flush = 0;
     bool ok = true;
@@ -345,36 +365,32 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       ok = wait_bounded(bar_sub_done + 8 * (si % T::kSubRing), (si / T::kSubRing) & 1, ctx, kStEpilogueAccFull);
       if (!ok) break;
       tcgen05_fence_after_sync();
-      constexpr int kLoadsPerSet = GS * TOK / 32;   // a set is read in loads of 32 columns
-      constexpr int kGroupsPerHalf = 32 / TOK;
+      // a set is read one group (TOK columns) per load
 #pragma unroll
-      for (int h = 0; h < kLoadsPerSet; ++h) {
-        uint32_t v[32];
-        tmem_ld_32x32(lane_addr + (si & 1) * (GS * TOK) + h * 32, v);
+      for (int j = 0; j < GS; ++j) {
+        uint32_t v[TOK];
+        if constexpr (TOK == 16) tmem_ld_32x16(lane_addr + (si & 1) * (GS * TOK) + j * TOK, v);
+        else tmem_ld_32x32(lane_addr + (si & 1) * (GS * TOK) + j * TOK, v);
         tmem_ld_wait();
-        if (h == kLoadsPerSet - 1) {
+        if (j == GS - 1) {
           tcgen05_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_acc_empty + 8 * (si & 1));   // the MMAs keep accumulating into the set
         }
+        if constexpr (DUMP) {
+          const int g = si * GS + j;
+          if (n_ok && g < nkb) {
 #pragma unroll
-        for (int jj = 0; jj < kGroupsPerHalf; ++jj) {
-          const int j = h * kGroupsPerHalf + jj;
-          if constexpr (DUMP) {
-            const int g = si * GS + j;
-            if (n_ok && g < nkb) {
-#pragma unroll
-              for (int t = 0; t < TOK; ++t)
-                if (m0 + t < p.M)
-                  p.partials[(static_cast<size_t>(kb_begin + g) * p.M + m0 + t) * p.N + n] =
-                      static_cast<int32_t>(v[jj * TOK + t]) - static_cast<int32_t>(bias);
-            }
+            for (int t = 0; t < TOK; ++t)
+              if (m0 + t < p.M)
+                p.partials[(static_cast<size_t>(kb_begin + g) * p.M + m0 + t) * p.N + n] =
+                    static_cast<int32_t>(v[t]) - static_cast<int32_t>(bias);
           }
-#pragma unroll
-          for (int t = 0; t < TOK; ++t) acc[t] = fmaf(c_cur[j], __uint_as_float(v[jj * TOK + t]), acc[t]);
-          s_sum += c_cur[j];
-          c_cur[j] = c_next[j];
         }
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) acc[t] = fmaf(c_cur[j], __uint_as_float(v[t]), acc[t]);
+        s_sum += c_cur[j];
+        c_cur[j] = c_next[j];
       }
       if (threadIdx.x == 0) SK_TRACE_EVENT(3, si);
       if (++flush == kBiasFlushGroups / GS) {
@@ -465,8 +481,22 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
           const int n = n0 + row;
           if (idx < rows * kTileN && m < p.M && n < p.N) {
             const float* src = red + (k * num_splits) * kTileN + row;
-            float sum = src[0];
-            for (int r = 1; r < num_splits; ++r) sum += src[r * kTileN];   // rank order: deterministic
+            // every load of an output is issued before the first add; the sum runs in rank order (deterministic)
+            float sum;
+            if (num_splits == 2) {
+              const float a0 = src[0], a1 = src[kTileN];
+              sum = a0 + a1;
+            } else if (num_splits == 4) {
+              const float a0 = src[0], a1 = src[kTileN], a2 = src[2 * kTileN], a3 = src[3 * kTileN];
+              sum = ((a0 + a1) + a2) + a3;
+            } else {
+              float a[8];
+#pragma unroll
+              for (int r = 0; r < 8; ++r) a[r] = src[r * kTileN];
+              sum = a[0];
+#pragma unroll
+              for (int r = 1; r < 8; ++r) sum += a[r];
+            }
             const float y = sum * xs[it];
             const uint16_t bits = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y))
                                              : __half_as_ushort(__float2half_rn(y));

@@ -111,6 +111,10 @@ class W2A8Plan:
     def device_status(self) -> int:
         return torch.ops.slimkernels.w2a8_plan_device_status(self._h)
 
+    def launch_floor_probe(self, M: int) -> None:
+        """Launches the empty kernel with the launch geometry of a decode-sized GEMM (measurement aid)."""
+        torch.ops.slimkernels.w2a8_plan_launch_floor_probe(self._h, self._w, int(M))
+
     def query_launch(self, M: int) -> dict:
         """The launch the plan makes for M tokens: token tile, split-K factor, CTAs and kernel kind
         (1 general tcgen05 kernel, 2 CUDA-core checker, 3 decode tcgen05 kernel)."""
