@@ -57,8 +57,10 @@ typedef enum sk_weight_layout {
 
 /* Keys of sk_w2a8_set_option (testing / tuning; 0 or SK_AUTO restores the heuristic). */
 typedef enum sk_option {
-  SK_OPT_KERNEL = 1,      /* 0 auto, 1 general tcgen05 kernel, 2 CUDA-core checker kernel (needs SK_WEIGHT_ROWMAJOR),
-                             3 decode tcgen05 kernel (group size 128; used for token tiles 16 / 32, else 1 is taken) */
+  SK_OPT_KERNEL = 1,      /* 0 auto, 1 general tcgen05 kernel (one CTA per tile), 2 CUDA-core checker kernel (needs
+                             SK_WEIGHT_ROWMAJOR), 3 decode tcgen05 kernel (group size 128; used for token tiles 16 / 32,
+                             else 1 is taken), 4 prefill tcgen05 kernel on pairs of CTAs (cta_group::2; group size 128, token
+                             tile 256, an even number of 128-feature tiles, else 1 is taken) */
   SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 / 192 / 256 */
   SK_OPT_SPLIT_K = 3,     /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
   SK_OPT_TMA_STORE = 6,   /* general kernel, one CTA per tile: 0 auto (= 2), 1 vector stores by the epilogue threads, 2 one TMA

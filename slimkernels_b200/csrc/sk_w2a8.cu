@@ -13,6 +13,7 @@
 #include "activation.cuh"
 #include "w2a8_umma.cuh"
 #include "w2a8_decode.cuh"
+#include "w2a8_pair.cuh"
 #include "weight_prep.cuh"
 
 namespace sk {
@@ -221,7 +222,8 @@ static long long* g_trace_buffer = nullptr;
 constexpr size_t kMapCache = 40;   // cached tensor maps per plan (activations and up to 8 output destinations)
 
 struct LaunchChoice {
-  int kernel;      // 1 tcgen05 (general), 2 CUDA-core checker, 3 tcgen05 (decode: token tiles 16 / 32, group size 128)
+  int kernel;      // 1 tcgen05 (general), 2 CUDA-core checker, 3 tcgen05 (decode: token tiles 16 / 32, group size 128),
+                   // 4 tcgen05 cta_group::2 (pairs of CTAs share a 256-token tile; group size 128, even number of feature tiles)
   int token_tile;  // 16 / 32 / 64 / 128
   int split_k;     // 1 / 2 / 4 / 8
   int persistent;  // 1: one resident set of CTAs walks all tiles
@@ -260,6 +262,13 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   c.persistent = (plan->opt_persistent == 2 && tiles > capacity) ? 1 : 0;
   if (c.split_k > 1 || (c.token_tile != 128 && c.token_tile != 256)) c.persistent = 0;
   c.ctas = static_cast<int>(c.persistent ? (tiles < capacity ? tiles : capacity) : tiles * c.split_k);
+  // Pairs of CTAs (cta_group::2) are an option (SK_OPT_KERNEL = 4), not the default: measured on B200 the pair
+  // kernel runs at ~1400 TOP/s where one CTA per tile runs at ~2300.  Its MMAs themselves run at full rate (128.8
+  // cycles per 256 x 256 x 32), but every hand-over between the two CTAs costs ~290 cycles (remote mbarrier arrival,
+  // multicast commit), two of them sit in the cycle MMA -> epilogue -> MMA of each of the two accumulator buffers that
+  // fit tensor memory at 256 tokens, and the epilogue is as long as the MMAs of a group.
+  const bool pair_ok = c.token_tile == 256 && plan->G == 128 && (plan->n_tiles % 2) == 0 && !c.persistent && c.split_k == 1;
+  if (c.kernel == 4 && !pair_ok) c.kernel = 1;
   return c;
 }
 
@@ -331,6 +340,36 @@ static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmP
   cfg.attrs = attr;
   cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, prm);
+  if (e != cudaSuccess) return cuda_fail(plan, e);
+  return SK_OK;
+}
+
+constexpr int kPairStages = 6;
+
+template <bool DUMP>
+static int launch_pair(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtensorMap& out_map,
+                       const ExtraOutMaps& extra_maps, const GemmParams& prm, int m_tiles, cudaStream_t stream) {
+  using L = PairTraits<kPairStages>;
+  auto kern = w2a8_pair_kernel<kPairStages, DUMP>;
+  static int configured_device_mask[64] = {0};
+  if (plan->device < 64 && !configured_device_mask[plan->device]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    if (e != cudaSuccess) return cuda_fail(plan, e);
+    configured_device_mask[plan->device] = 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan->n_tiles, m_tiles, 1);
+  cfg.blockDim = dim3(L::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kDynamicBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;      // the two CTAs of a pair: adjacent feature tiles, same token tile
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, out_map, extra_maps, prm);
   if (e != cudaSuccess) return cuda_fail(plan, e);
   return SK_OK;
 }
@@ -491,7 +530,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
     }
   } else {
     CUtensorMap map;
-    rc = get_x_map(plan, x_q, M, ld_x, ch.token_tile, &map);
+    rc = get_x_map(plan, x_q, M, ld_x, ch.kernel == 4 ? 128 : ch.token_tile, &map);
     if (rc == SK_OK) {
       GemmParams prm;
       prm.w_tiled = plan->w_tiled;
@@ -539,7 +578,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       // One CTA per tile: the staged tile leaves through one TMA store per destination where the buffers allow it
       // (16-byte aligned, pitch a multiple of 8 elements, N a multiple of 8).
       prm.tma_out = 0;
-      if (!persist && !partials && ch.kernel == 1 && ch.split_k == 1 && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
+      if (!persist && !partials && (ch.kernel == 1 || ch.kernel == 4) && ch.split_k == 1 && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
           (reinterpret_cast<uintptr_t>(out) & 15) == 0 && plan->opt_tma_store != 1) {
         bool ok = get_out_map(plan, out, M, ld_out, ch.token_tile, &out_map) == SK_OK;
         for (int i = 0; ok && i < n_extra; ++i)
@@ -552,6 +591,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
         if (ch.kernel == 3)
           rc = ch.token_tile == 16 ? launch_decode<16, true>(plan, map, prm, m_tiles, 1, stream)
                                    : launch_decode<32, true>(plan, map, prm, m_tiles, 1, stream);
+        else if (ch.kernel == 4) rc = launch_pair<true>(plan, map, out_map, extra_maps, prm, m_tiles, stream);
         else rc = dispatch_umma<true>(plan, ch.token_tile, map, out_map, extra_maps, prm, m_tiles, 1, 0, stream);
         if (rc == SK_OK) {
           const long long mn = M * plan->N;
@@ -564,6 +604,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       else if (ch.kernel == 3)
         rc = ch.token_tile == 16 ? launch_decode<16, false>(plan, map, prm, m_tiles, ch.split_k, stream)
                                  : launch_decode<32, false>(plan, map, prm, m_tiles, ch.split_k, stream);
+      else if (ch.kernel == 4) rc = launch_pair<false>(plan, map, out_map, extra_maps, prm, m_tiles, stream);
       else rc = dispatch_umma<false>(plan, ch.token_tile, map, out_map, extra_maps, prm, m_tiles, ch.split_k, persist ? ch.ctas : 0, stream);
     }
   }
@@ -738,8 +779,9 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
   if (!plan) return SK_ERR_NULL_POINTER;
   switch (key) {
     case SK_OPT_KERNEL:
-      if (value < 0 || value > 3) return SK_ERR_BAD_ARGUMENT;
+      if (value < 0 || value > 4) return SK_ERR_BAD_ARGUMENT;
       if (value == 2 && !plan->w_rowmajor) return SK_ERR_UNAVAILABLE;
+      if (value == 4 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       if (value == 3 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       plan->opt_kernel = static_cast<int>(value);
       return SK_OK;

@@ -34,24 +34,6 @@
 
 namespace sk {
 
-// Bounded wait for a role that is not on the critical path of a K block: sleeps between polls, so that it does not
-// take issue slots and integer-pipe cycles from the warps that expand (the expansion saturates the integer pipe).
-__device__ __forceinline__ bool wait_bounded_relaxed(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code,
-                                                     unsigned sleep_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*ctx.abort_flag) return false;
-    if (clock64() - t0 > ctx.limit) {
-      *ctx.abort_flag = 1;
-      atomicCAS(ctx.status, 0, code);
-      return false;
-    }
-  }
-}
-
 template <int TOK>
 struct DecodeTraits {
   static_assert(TOK == 16 || TOK == 32, "token tile of the decode kernel");

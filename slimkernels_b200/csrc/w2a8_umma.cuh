@@ -211,6 +211,24 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
   return wait_slow(bar, parity, ctx.abort_flag, ctx.status, code, ctx.limit);
 }
 
+// Bounded wait for a role that is not on the critical path of a K block: sleeps between polls, so that it does not
+// take issue slots and integer-pipe cycles from the warps that expand (the expansion saturates the integer pipe).
+__device__ __forceinline__ bool wait_bounded_relaxed(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int code,
+                                                     unsigned sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*ctx.abort_flag) return false;
+    if (clock64() - t0 > ctx.limit) {
+      *ctx.abort_flag = 1;
+      atomicCAS(ctx.status, 0, code);
+      return false;
+    }
+  }
+}
+
 // 16 two-bit codes held in `w` as  sum_{j,b} code[4j+b] << (4b + 2(j&1) + 16(j>>1))  ->  16 int8 bytes
 // lut[code] in memory order; lut = the four bytes (0-zp, 1-zp, 2-zp, 3-zp).
 __device__ __forceinline__ uint4 expand16(uint32_t w, uint32_t lut) {
@@ -385,7 +403,7 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const int m0 = tc.m_tile * BLOCK_M;
         const uint8_t* wsrc = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
         for (int kcoord = kb_begin * kBlockK; kcoord < kb_end * kBlockK; kcoord += kBlockK) {
-          ok = wait_bounded(empty, phase ^ 1, ctx, kStProducerEmpty);
+          ok = wait_bounded_relaxed(empty, phase ^ 1, ctx, kStProducerEmpty, 100);   // not urgent: the ring is several K blocks deep
           if (!ok) break;
           if (elect_one() && kcoord != (kb_begin + p.fault_skip_kb) * kBlockK) {
             SK_TRACE_EVENT(0, issued);

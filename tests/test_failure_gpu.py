@@ -30,6 +30,7 @@ WAITS_FOR_COPIES = {0x21: "expander", 0x31: "MMA issuer"}
 @pytest.mark.parametrize("kernel,M,skip", [
     (capi.KERNEL_TCGEN05, 40, 2),             # general kernel, 64-token tile: K block 1 of 8 never arrives
     (capi.KERNEL_TCGEN05, 300, 1),            # 256-token tile, two token tiles, first K block
+    (capi.KERNEL_TCGEN05_PAIR, 300, 3),       # pairs of CTAs (cta_group::2): both CTAs of every pair give up and leave
     (capi.KERNEL_TCGEN05_DECODE, 16, 1),      # decode kernel: the first load stage (K blocks 0..3)
     (capi.KERNEL_TCGEN05_DECODE, 16, 5),      # decode kernel: the second load stage
 ])

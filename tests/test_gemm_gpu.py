@@ -145,6 +145,33 @@ def test_tma_store_output_matches_thread_stores(token_tile, M, N):
     assert np.abs(y_tma[:, :N] - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (300, 1000, 640), (700, 1280, 1408), (1025, 512, 4096), (130, 256, 256)])
+def test_pair_kernel_against_oracle_and_single_cta_kernel(M, N, K):
+    """The prefill kernel on pairs of CTAs (cta_group::2: two CTAs share a 256-token tile, each loading half of it):
+    ragged token and feature edges, one and many K blocks; outputs bit-identical to the one-CTA kernel (same
+    arithmetic in the same order), integer partial sums bit-exact."""
+    prob = random_problem(M, N, K, 128, seed=M + K)
+    x_q, xs, wp, ws = prob
+    dp = DeviceProblem(x_q, xs, wp, ws).force(kernel=capi.KERNEL_TCGEN05_PAIR, token_tile=256)
+    assert dp.plan.query_launch(M)["kernel"] == capi.KERNEL_TCGEN05_PAIR
+    y_pair = dp.gemm(ld_out=N + 8)
+    p_pair = to_np(dp.partials())
+    y_one = dp.force(kernel=capi.KERNEL_TCGEN05, token_tile=256).gemm(ld_out=N + 8)
+    assert dp.plan.query_launch(M)["kernel"] == capi.KERNEL_TCGEN05
+    assert torch.equal(y_pair[:, :N], y_one[:, :N])
+    assert torch.isnan(y_pair[:, N:]).all()
+    assert np.abs(to_np(y_pair)[:, :N] - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+    np.testing.assert_array_equal(p_pair, O.w2a8_partials(x_q, wp, 128))
+
+
+def test_pair_kernel_needs_an_even_number_of_feature_tiles():
+    x_q, xs, wp, ws = random_problem(300, 384, 256, 128, seed=12)      # three feature tiles: one CTA per tile
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    assert dp.plan.query_launch(300)["kernel"] == capi.KERNEL_TCGEN05
+    assert dp.force(kernel=capi.KERNEL_TCGEN05_PAIR).plan.query_launch(300)["kernel"] == capi.KERNEL_TCGEN05
+    assert np.abs(to_np(dp.gemm()) - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+
+
 def test_checker_kernel_matches_oracle():
     prob = random_problem(19, 200, 512, 128, seed=5)
     _check(prob, force=dict(kernel=capi.KERNEL_CUDA_CORE))
