@@ -946,7 +946,18 @@ int sk_w2a8_quantize_weight(const float* w, int64_t ld_w, int64_t K, int64_t N, 
       (scale_f32 && (reinterpret_cast<uintptr_t>(scale_f32) & 3)))
     return SK_ERR_BAD_ALIGNMENT;
   const dim3 grid(static_cast<unsigned>((N + sk::kPrepThreads - 1) / sk::kPrepThreads), static_cast<unsigned>(K / group_size));
-  sk::quantize_pack_weight_kernel<<<grid, sk::kPrepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  constexpr int kPrepSmem = sk::kPrepSlab * sk::kPrepThreads * 4;     // 64 KiB
+  static int prep_configured[64] = {0};
+  int prep_dev = 0;
+  if (cudaGetDevice(&prep_dev) != cudaSuccess) return SK_ERR_CUDA;
+  if (prep_dev >= 0 && prep_dev < 64 && !prep_configured[prep_dev]) {
+    if (cudaFuncSetAttribute(sk::quantize_pack_weight_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return SK_ERR_CUDA;
+    }
+    prep_configured[prep_dev] = 1;
+  }
+  sk::quantize_pack_weight_kernel<<<grid, sk::kPrepCtaThreads, kPrepSmem, static_cast<cudaStream_t>(stream)>>>(
       w, ld_w, static_cast<int>(K), static_cast<int>(N), group_size, w_packed, scale_f32, static_cast<__half*>(scale_f16));
   if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
   return SK_OK;
@@ -963,6 +974,8 @@ int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int6
   const dim3 grid(static_cast<unsigned>(M));
   if (K <= 8 * sk::kActThreads * 2)
     sk::quantize_activation_kernel<2><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
+  else if (K <= 8 * sk::kActThreads * 4)
+    sk::quantize_activation_kernel<4><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
   else
     sk::quantize_activation_kernel<8><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
   if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
@@ -978,12 +991,35 @@ int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M,
     return SK_ERR_BAD_ALIGNMENT;
   const auto st = static_cast<cudaStream_t>(stream);
   const __half* gu = static_cast<const __half*>(gate_up_f16);
-  if (4 * I <= 24 * 1024)    // short rows: the fp32 row stays in shared memory between the two passes (>= 8 CTAs per SM)
-    sk::silu_mul_quantize_kernel<<<static_cast<unsigned>(M), sk::kActThreads, static_cast<int>(4 * I), st>>>(
-        gu, ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
-  else                       // long rows: read twice and recompute (same values), full occupancy
-    sk::silu_mul_quantize_twopass_kernel<<<static_cast<unsigned>(M), sk::kActThreads, 0, st>>>(
-        gu, ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
+  // one pass over HBM: the row split over a cluster of 1..8 CTAs whose threads keep their fp32 values in registers
+  const long long per_cta = 8LL * sk::kActThreads * sk::kClusterVecs;
+  int csize = 1;
+  while (csize < 8 && I > per_cta * csize) csize *= 2;
+  if (I <= per_cta * csize) {
+    for (int64_t m0 = 0; m0 < M; m0 += 65535) {       // gridDim.y holds at most 65535 rows per launch
+      const int64_t rows = M - m0 < 65535 ? M - m0 : 65535;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(csize), static_cast<unsigned>(rows), 1);
+      cfg.blockDim = dim3(sk::kActThreads, 1, 1);
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (cudaLaunchKernelEx(&cfg, sk::silu_mul_quantize_cluster_kernel, gu + m0 * ld_gu, static_cast<long long>(ld_gu),
+                             h_q + m0 * ld_q, static_cast<long long>(ld_q), h_scale + m0, static_cast<int>(I)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return SK_ERR_CUDA;
+      }
+    }
+    return SK_OK;
+  }
+  // longer rows still: read twice and recompute (same values), full occupancy
+  sk::silu_mul_quantize_twopass_kernel<<<static_cast<unsigned>(M), sk::kActThreads, 0, st>>>(
+      gu, ld_gu, h_q, ld_q, h_scale, static_cast<int>(I));
   if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
   return SK_OK;
 }
