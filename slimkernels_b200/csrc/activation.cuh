@@ -14,6 +14,12 @@ namespace sk {
 
 constexpr int kActThreads = 256;
 
+// Programmatic dependent launch (both are no-ops for a kernel launched without the attribute): the next kernel in the
+// stream may start its own set-up now -- the decode GEMM that follows a quantiser uses that to stream its first
+// weights --, and this kernel's inputs, which the previous kernel wrote, are read only after that kernel is complete.
+__device__ __forceinline__ void act_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void act_wait_for_inputs() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float block_max(float v, float* red /* [kActThreads / 32] */) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -59,6 +65,8 @@ __global__ void __launch_bounds__(kActThreads)
 quantize_activation_kernel(const __half* __restrict__ x, long long ld_x, int8_t* __restrict__ x_q, long long ld_q,
                            float* __restrict__ x_scale, int K) {
   __shared__ float red[kActThreads / 32];
+  act_launch_dependents();
+  act_wait_for_inputs();
   const long long m = blockIdx.x;
   const uint4* row = reinterpret_cast<const uint4*>(x + m * ld_x);
   const int nvec = K / 8;
@@ -132,6 +140,8 @@ silu_mul_quantize_cluster_kernel(const __half* __restrict__ gate_up, long long l
                                  long long ld_q, float* __restrict__ h_scale, int I) {
   __shared__ float red[kActThreads / 32];
   __shared__ float part[8];                     // partial maxima of the cluster's CTAs
+  act_launch_dependents();
+  act_wait_for_inputs();
   const long long m = blockIdx.y;
   const int csize = static_cast<int>(gridDim.x);   // the cluster spans the grid's x dimension
   const int crank = static_cast<int>(blockIdx.x);
@@ -195,6 +205,8 @@ __global__ void __launch_bounds__(kActThreads)
 silu_mul_quantize_twopass_kernel(const __half* __restrict__ gate_up, long long ld_gu, int8_t* __restrict__ h_q,
                                  long long ld_q, float* __restrict__ h_scale, int I) {
   __shared__ float red[kActThreads / 32];
+  act_launch_dependents();
+  act_wait_for_inputs();
   const long long m = blockIdx.x;
   const uint4* g = reinterpret_cast<const uint4*>(gate_up + m * ld_gu);
   const uint4* u = reinterpret_cast<const uint4*>(gate_up + m * ld_gu + I);

@@ -972,12 +972,24 @@ int sk_quantize_activation_int8(const void* x_f16, int64_t ld_x, int64_t M, int6
   auto st = static_cast<cudaStream_t>(stream);
   const __half* x = static_cast<const __half*>(x_f16);
   const dim3 grid(static_cast<unsigned>(M));
-  if (K <= 8 * sk::kActThreads * 2)
-    sk::quantize_activation_kernel<2><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
-  else if (K <= 8 * sk::kActThreads * 4)
-    sk::quantize_activation_kernel<4><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
-  else
-    sk::quantize_activation_kernel<8><<<grid, sk::kActThreads, 0, st>>>(x, ld_x, x_q, ld_q, x_scale, static_cast<int>(K));
+  // launched as a programmatic dependent launch: the kernel waits for its inputs itself (griddepcontrol.wait) and
+  // lets the kernel behind it start its set-up early
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(sk::kActThreads, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const long long ldx = ld_x, ldq = ld_q;
+  const int k = static_cast<int>(K);
+  cudaError_t le;
+  if (K <= 8 * sk::kActThreads * 2) le = cudaLaunchKernelEx(&cfg, sk::quantize_activation_kernel<2>, x, ldx, x_q, ldq, x_scale, k);
+  else if (K <= 8 * sk::kActThreads * 4) le = cudaLaunchKernelEx(&cfg, sk::quantize_activation_kernel<4>, x, ldx, x_q, ldq, x_scale, k);
+  else le = cudaLaunchKernelEx(&cfg, sk::quantize_activation_kernel<8>, x, ldx, x_q, ldq, x_scale, k);
+  if (le != cudaSuccess) { (void)cudaGetLastError(); return SK_ERR_CUDA; }
   if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
   return SK_OK;
 }
@@ -1002,13 +1014,15 @@ int sk_silu_mul_quantize_int8(const void* gate_up_f16, int64_t ld_gu, int64_t M,
       cfg.gridDim = dim3(static_cast<unsigned>(csize), static_cast<unsigned>(rows), 1);
       cfg.blockDim = dim3(sk::kActThreads, 1, 1);
       cfg.stream = st;
-      cudaLaunchAttribute attr[1];
+      cudaLaunchAttribute attr[2];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
       attr[0].val.clusterDim.y = 1;
       attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see sk_quantize_activation_int8
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
-      cfg.numAttrs = 1;
+      cfg.numAttrs = 2;
       if (cudaLaunchKernelEx(&cfg, sk::silu_mul_quantize_cluster_kernel, gu + m0 * ld_gu, static_cast<long long>(ld_gu),
                              h_q + m0 * ld_q, static_cast<long long>(ld_q), h_scale + m0, static_cast<int>(I)) != cudaSuccess) {
         (void)cudaGetLastError();
