@@ -63,6 +63,66 @@ def test_two_gpu_shard_and_allgather(built_libs, fused):
         assert err <= 1e-2
 
 
+def _worker_overlap(rank, world, port, q):
+    """Fused exchange, three steps in a row with different activations: the result of step 1 is read on a SIDE stream
+    while step 2 runs (two output buffers alternate, so step 2 writes elsewhere), and step 3 -- which reuses step 1's
+    buffer -- is launched only after that reader is done."""
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from oracle import w2a8_oracle as O
+        from slimkernels_b200 import workloads as W
+        from slimkernels_b200.torch.sharded import ShardedW2A8Gemm, shard_weight
+        M, N, K, G = 512, 2048, 1024, 128
+        _, _, w_packed, w_scale = W.make_problem(M, N, K, G, seed=0)
+        wl, sl = shard_weight(torch.from_numpy(w_packed).to(dev), torch.from_numpy(w_scale).to(dev), world, rank)
+        op = ShardedW2A8Gemm(wl, sl, N, group_size=G, fused=True)
+        xs_np = [W.make_activation(M, K, seed=10 + i) for i in range(3)]
+        xs = [(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev)) for a, b in xs_np]
+        refs = [O.w2a8_gemm_dequant_path(a, b, w_packed, w_scale, G) for a, b in xs_np]
+        main, side = torch.cuda.current_stream(dev), torch.cuda.Stream(dev)
+        errs = []
+        for rep in range(4):                         # several rounds, so that the ranks drift apart if they can
+            y1 = op(*xs[0])
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                c1 = y1.float() * 1.0                # the consumer of step 1, concurrent with step 2
+            y2 = op(*xs[1])                          # other buffer
+            c2 = y2.float() * 1.0
+            main.wait_stream(side)                   # step 3 reuses step 1's buffer: order it behind the reader
+            y3 = op(*xs[2])
+            assert y3.data_ptr() == y1.data_ptr() and y2.data_ptr() != y1.data_ptr()
+            c3 = y3.float() * 1.0
+            torch.cuda.synchronize(dev)
+            errs.append(max(float(np.abs(c.cpu().numpy() - r).max()) for c, r in zip((c1, c2, c3), refs)))
+        q.put((rank, max(errs)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_fused_result_can_be_read_while_the_next_step_runs(built_libs):
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_overlap, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for _, err in results:
+        assert err <= 1e-2
+
+
 def _worker_k(rank, world, port, q):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
