@@ -58,9 +58,14 @@ typedef enum sk_weight_layout {
 /* Keys of sk_w2a8_set_option (testing / tuning; 0 or SK_AUTO restores the heuristic). */
 typedef enum sk_option {
   SK_OPT_KERNEL = 1,      /* 0 auto, 1 general tcgen05 kernel (one CTA per tile), 2 CUDA-core checker kernel (needs
-                             SK_WEIGHT_ROWMAJOR), 3 decode tcgen05 kernel (group size 128; used for token tiles 16 / 32,
-                             else 1 is taken), 4 prefill tcgen05 kernel on pairs of CTAs (cta_group::2; group size 128, token
-                             tile 256, an even number of 128-feature tiles, else 1 is taken) */
+                             SK_WEIGHT_ROWMAJOR), 3 decode tcgen05 kernel that gives a CTA one feature tile or 1/2, 1/4, 1/8
+                             of its K range, summed over a cluster (group size 128; used for token tiles 16 / 32, else 1 is
+                             taken), 4 prefill tcgen05 kernel on pairs of CTAs (cta_group::2; group size 128, token tile 256, an
+                             even number of 128-feature tiles, else 1 is taken), 5 decode tcgen05 kernel that cuts the K
+                             range of the WHOLE problem into equal CTA ranges, two CTAs per SM (the default for M <= 32
+                             with group size 128 and K a multiple of 256; else 3 is taken).  Partial sums of tiles that
+                             two or more CTAs share meet in a scratch buffer owned by the plan, so calls on one plan
+                             must not run concurrently (they must not anyway, see above). */
   SK_OPT_TOKEN_TILE = 2,  /* tokens per CTA tile: 0 auto, or 16 / 32 / 64 / 128 / 192 / 256 */
   SK_OPT_SPLIT_K = 3,     /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
   SK_OPT_TMA_STORE = 6,   /* general kernel, one CTA per tile: 0 auto (= 2), 1 vector stores by the epilogue threads, 2 one TMA
@@ -72,7 +77,9 @@ typedef enum sk_option {
                              128 / 256 without split-K, when there are more tiles than the GPU holds at once) */
   SK_OPT_WAIT_LIMIT_CYCLES = 7, /* SM cycles after which a wait inside a kernel gives up and the kernel returns with a
                              device status (0 = default, 1e9 cycles, about half a second; otherwise >= 1000) */
-  SK_OPT_TEST_SKIP_COPY = 8 /* failure-path test hook, 0 = off: with value v > 0 the producer of every CTA leaves out
+  SK_OPT_STREAM_CTAS = 9, /* kernel 5: CTAs the problem is cut into; 0 auto (two per SM, at least two K blocks each).
+                             Reallocates the plan's scratch buffer: a set-up call, not for the call path. */
+  SK_OPT_TEST_SKIP_COPY = 8, /* failure-path test hook, 0 = off: with value v > 0 the producer of every CTA leaves out
                              the copies of K block v - 1 of its range, so the waits for them run into the limit, the
                              kernel returns and sk_w2a8_last_device_status reports which wait gave up.  The output
                              of such a launch is undefined.  Nothing traps or faults. */
@@ -92,7 +99,11 @@ int sk_w2a8_unrepack(const uint8_t* w_tiled, int64_t N, int64_t K, uint8_t* w_pa
 /* -------- plan ------------------------------------------------------------------------------------
  * Binds one weight matrix to a device: validates shapes/alignment, builds the tiled weight copy (or
  * borrows one), allocates a 4-byte device status word.  Stands where gemm_tn builds its tilers, smem
- * layouts and tensor maps on every call (wgmma_sm90_W2A8.cu:448-466).  Synchronises `device` once. */
+ * layouts and tensor maps on every call (wgmma_sm90_W2A8.cu:448-466).  Synchronises `device` once.
+ * With group size 128 the plan also makes a private copy of the scales in the order its decode kernels
+ * stream them, and a scratch buffer for partial sums of its balanced-split decode kernel (a few MiB):
+ * w_scale_f16 must still outlive the plan (the other kernels read it), and a change of its contents
+ * after plan creation is not picked up consistently -- make a new plan instead. */
 int sk_w2a8_plan_create(sk_w2a8_plan** plan, int device, int64_t N, int64_t K, int group_size,
                         int zero_point, const uint8_t* w, int w_layout, const void* w_scale_f16,
                         int out_dtype);

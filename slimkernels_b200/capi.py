@@ -25,8 +25,8 @@ SK_ERR_STATIC_SCRATCH_TOO_SMALL = -10
 SK_OUT_F16, SK_OUT_BF16 = 0, 1
 SK_WEIGHT_ROWMAJOR, SK_WEIGHT_TILED = 0, 1
 SK_OPT_KERNEL, SK_OPT_TOKEN_TILE, SK_OPT_SPLIT_K, SK_OPT_PERSISTENT, SK_OPT_DEPENDENT_LAUNCH, SK_OPT_TMA_STORE = 1, 2, 3, 4, 5, 6
-SK_OPT_WAIT_LIMIT_CYCLES, SK_OPT_TEST_SKIP_COPY = 7, 8
-KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_CUDA_CORE, KERNEL_TCGEN05_DECODE, KERNEL_TCGEN05_PAIR = 0, 1, 2, 3, 4
+SK_OPT_WAIT_LIMIT_CYCLES, SK_OPT_TEST_SKIP_COPY, SK_OPT_STREAM_CTAS = 7, 8, 9
+KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_CUDA_CORE, KERNEL_TCGEN05_DECODE, KERNEL_TCGEN05_PAIR, KERNEL_TCGEN05_DECODE_BALANCED = 0, 1, 2, 3, 4, 5
 
 _i64, _int, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
 

@@ -13,6 +13,7 @@
 #include "activation.cuh"
 #include "w2a8_umma.cuh"
 #include "w2a8_decode.cuh"
+#include "w2a8_stream.cuh"
 #include "w2a8_pair.cuh"
 #include "weight_prep.cuh"
 
@@ -198,7 +199,12 @@ struct sk_w2a8_plan {
   const uint8_t* w_tiled = nullptr;     // owned or borrowed
   uint8_t* w_tiled_owned = nullptr;
   const __half* w_scale = nullptr;      // borrowed
+  __half* w_scale_tiled = nullptr;      // device, owned: [n_tiles][k_blocks][128] copy of the scales (group size 128 only)
   int* status = nullptr;                // device, owned
+  // balanced-split decode kernel: scratch for the partial sums of tiles shared between CTAs, and their counters
+  float* stream_scratch = nullptr;      // device, owned (null: that kernel is not available for this plan)
+  int* stream_counters = nullptr;       // device, owned; zero between launches
+  int stream_ctas = 0, stream_slots = 0;
   int last_cuda_error = 0;
   int opt_kernel = 0, opt_token_tile = 0, opt_split_k = 0, opt_persistent = 0, opt_pdl = 0, opt_tma_store = 0;
   long long opt_wait_limit = 0;         // 0: the default limit
@@ -223,7 +229,8 @@ constexpr size_t kMapCache = 40;   // cached tensor maps per plan (activations a
 
 struct LaunchChoice {
   int kernel;      // 1 tcgen05 (general), 2 CUDA-core checker, 3 tcgen05 (decode: token tiles 16 / 32, group size 128),
-                   // 4 tcgen05 cta_group::2 (pairs of CTAs share a 256-token tile; group size 128, even number of feature tiles)
+                   // 4 tcgen05 cta_group::2 (pairs of CTAs share a 256-token tile; group size 128, even number of feature tiles),
+                   // 5 tcgen05 (decode, one token tile, K range of the whole problem cut into equal CTA ranges)
   int token_tile;  // 16 / 32 / 64 / 128
   int split_k;     // 1 / 2 / 4 / 8
   int persistent;  // 1: one resident set of CTAs walks all tiles
@@ -235,9 +242,24 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   if (plan->opt_token_tile) c.token_tile = plan->opt_token_tile;
   else c.token_tile = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const bool decode_ok = plan->G == 128 && c.token_tile <= 32;
-  c.kernel = plan->opt_kernel ? plan->opt_kernel : (decode_ok ? 3 : 1);
+  // Decode sizes that are one token tile go to the balanced-split kernel (5) when the plan has its scratch buffer;
+  // a forced split (SK_OPT_SPLIT_K) or several token tiles go to the kernel that splits over clusters (3).
+  const bool stream_ok = decode_ok && M <= c.token_tile && plan->stream_scratch != nullptr && plan->opt_split_k <= 1;
+  // Measured on B200 (M = 16): the balanced split wins once every SM has ~64 K blocks or more to stream (70B-class
+  // projections: 53 against 70 us on 57344 x 8192); below that its longer tail -- partial sums meet in L2, three
+  // global round trips -- costs more than the even load saves.  Its 32-token variant is slower throughout.
+  const bool stream_pays = stream_ok && c.token_tile == 16 &&
+                           static_cast<long long>(plan->n_tiles) * plan->k_blocks >= 64LL * plan->sm_count;
+  c.kernel = plan->opt_kernel ? plan->opt_kernel : (stream_pays ? 5 : decode_ok ? 3 : 1);
+  if (c.kernel == 5 && !stream_ok) c.kernel = 3;
   if (c.kernel == 3 && !decode_ok) c.kernel = 1;
   const int groups = static_cast<int>(plan->K / plan->G);
+  if (c.kernel == 5) {
+    c.split_k = 1;
+    c.persistent = 0;
+    c.ctas = plan->stream_ctas;
+    return c;
+  }
   if (plan->opt_split_k) c.split_k = plan->opt_split_k;
   else {
     // Fill the machine in ONE wave: split the K range of a tile over a cluster while the CTAs still fit the
@@ -344,6 +366,85 @@ static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmP
   return SK_OK;
 }
 
+template <int TOK, int EXP_WARPS>
+static int launch_stream(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, cudaStream_t stream) {
+  using L = StreamTraits<TOK, EXP_WARPS>;
+  auto kern = w2a8_stream_kernel<TOK, EXP_WARPS>;
+  static int configured_device_mask[64] = {0};
+  if (plan->device < 64 && !configured_device_mask[plan->device]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    if (e != cudaSuccess) return cuda_fail(plan, e);
+    configured_device_mask[plan->device] = 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan->stream_ctas, 1, 1);
+  cfg.blockDim = dim3(L::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kDynamicBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (plan->opt_pdl != 1) {   // programmatic dependent launch, as for the other decode kernel
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, prm);
+  if (e != cudaSuccess) return cuda_fail(plan, e);
+  return SK_OK;
+}
+
+static int dispatch_stream(sk_w2a8_plan* plan, int token_tile, const CUtensorMap& map, const GemmParams& prm,
+                           cudaStream_t stream) {
+  // (the kernel can be built with 8 or 16 expander warps and one CTA per SM; measured on B200 that is slower than
+  // two CTAs of four expander warps per SM)
+  return token_tile == 16 ? launch_stream<16, 4>(plan, map, prm, stream) : launch_stream<32, 4>(plan, map, prm, stream);
+}
+
+// Geometry of the balanced-split decode kernel for a plan: how many CTAs, and the most CTAs that share one tile.
+// want_ctas = 0: two CTAs per SM, but no CTA with less than one half stage.
+static void stream_geometry(const sk_w2a8_plan* plan, int want_ctas, int* ctas_out, int* slots_out) {
+  const int units_per_tile = plan->k_blocks / 2;
+  const long long units = static_cast<long long>(plan->n_tiles) * units_per_tile;
+  long long ctas = want_ctas > 0 ? want_ctas : 2LL * plan->sm_count;
+  if (ctas > units) ctas = units;
+  int slots = 1;
+  for (long long t = 0; t < plan->n_tiles; ++t) {
+    const int first = stream_owner(units, static_cast<int>(ctas), t * units_per_tile);
+    const int last = stream_owner(units, static_cast<int>(ctas), (t + 1) * units_per_tile - 1);
+    if (last - first + 1 > slots) slots = last - first + 1;
+  }
+  *ctas_out = static_cast<int>(ctas);
+  *slots_out = slots;
+}
+
+// (Re)allocates the scratch buffer and the counters of the balanced-split decode kernel.  Not on the call path: plan
+// creation and sk_w2a8_set_option only.  The device of the plan is current.
+static int stream_setup(sk_w2a8_plan* plan, int want_ctas) {
+  if (plan->stream_scratch) { cudaFree(plan->stream_scratch); plan->stream_scratch = nullptr; }
+  if (plan->stream_counters) { cudaFree(plan->stream_counters); plan->stream_counters = nullptr; }
+  plan->stream_ctas = plan->stream_slots = 0;
+  if (plan->G != 128 || (plan->K % 256) != 0) return SK_OK;   // whole half stages only: the other decode kernel serves the rest
+  int ctas = 0, slots = 0;
+  stream_geometry(plan, want_ctas, &ctas, &slots);
+  const size_t bytes = static_cast<size_t>(plan->n_tiles) * slots * StreamTraits<32>::kSlotFloats * sizeof(float);
+  cudaError_t e = cudaMalloc(&plan->stream_scratch, bytes);
+  if (e != cudaSuccess) { plan->stream_scratch = nullptr; return cuda_fail(plan, e); }
+  const size_t cbytes = static_cast<size_t>(plan->n_tiles) * StreamTraits<32>::kEpiWarps * sizeof(int);
+  e = cudaMalloc(&plan->stream_counters, cbytes);
+  if (e == cudaSuccess) e = cudaMemset(plan->stream_counters, 0, cbytes);
+  if (e != cudaSuccess) {
+    cudaFree(plan->stream_scratch);
+    plan->stream_scratch = nullptr;
+    if (plan->stream_counters) { cudaFree(plan->stream_counters); plan->stream_counters = nullptr; }
+    return cuda_fail(plan, e);
+  }
+  plan->stream_ctas = ctas;
+  plan->stream_slots = slots;
+  return SK_OK;
+}
+
 constexpr int kPairStages = 6;
 
 template <bool DUMP>
@@ -377,7 +478,7 @@ static int launch_pair(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtenso
 constexpr int kAccBufsSmall = 4;   // accumulator buffers of the token tiles <= 128
 constexpr int kAccBufs256 = 2;     // 2 x 256 columns fill the tensor memory
 static int acc_bufs_of(int token_tile, int kernel) {
-  if (kernel == 3) return token_tile == 16 ? DecodeTraits<16>::kAccBufs : DecodeTraits<32>::kAccBufs;
+  if (kernel == 3 || kernel == 5) return token_tile == 16 ? DecodeTraits<16>::kAccBufs : DecodeTraits<32>::kAccBufs;
   return token_tile >= 192 ? kAccBufs256 : kAccBufsSmall;
 }
 
@@ -397,7 +498,10 @@ static bool running_sum_fits(const sk_w2a8_plan* plan, int token_tile, int split
 // beyond that the call is refused.
 static int resolve_launch(const sk_w2a8_plan* plan, long long M, bool debug_partials, LaunchChoice* out) {
   LaunchChoice ch = choose(plan, M);
-  if (debug_partials) { ch.split_k = 1; ch.persistent = 0; }
+  if (debug_partials) {
+    if (ch.kernel == 5) { ch.kernel = 3; ch.ctas = static_cast<int>(plan->n_tiles * ((M + ch.token_tile - 1) / ch.token_tile)); }
+    ch.split_k = 1; ch.persistent = 0;
+  }
   if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k, ch.kernel)) {
     if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1, 1)) {
       ch.token_tile = 128;
@@ -409,6 +513,20 @@ static int resolve_launch(const sk_w2a8_plan* plan, long long M, bool debug_part
   }
   *out = ch;
   return SK_OK;
+}
+
+// The scales of a group-size-128 plan in the order the decode kernels stream them: [n_tiles][k_blocks][128 features]
+// (rows past N are zero), so that the scales of a CTA's K range are one contiguous run.
+__global__ void tile_scales_kernel(const __half* __restrict__ w_scale, __half* __restrict__ tiled, long long N,
+                                   int k_blocks, long long total) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i % kTileN);
+    const long long t = i / kTileN;
+    const int kb = static_cast<int>(t % k_blocks);
+    const long long n = (t / k_blocks) * kTileN + r;
+    tiled[i] = n < N ? w_scale[static_cast<size_t>(kb) * N + n] : __float2half(0.f);
+  }
 }
 
 // partials[g] holds the running sum of its accumulator buffer; turn it into the group's own partial sum.
@@ -535,6 +653,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       GemmParams prm;
       prm.w_tiled = plan->w_tiled;
       prm.w_scale = plan->w_scale;
+      prm.w_scale_tiled = plan->w_scale_tiled;
       prm.x_scale = x_scale;
       prm.out = out;
       prm.n_extra = n_extra;
@@ -552,6 +671,9 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.out_bf16 = plan->out_dtype == SK_OUT_BF16;
       prm.wait_limit = plan->opt_wait_limit > 0 ? plan->opt_wait_limit : kWaitLimitCycles;
       prm.fault_skip_kb = plan->opt_skip_copy - 1;
+      prm.stream_scratch = plan->stream_scratch;
+      prm.stream_counters = plan->stream_counters;
+      prm.stream_slots = plan->stream_slots;
 #ifdef SK_TRACE
       prm.trace = g_trace_buffer;
 #endif
@@ -601,6 +723,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
           if (e != cudaSuccess) rc = cuda_fail(plan, e);
         }
       }
+      else if (ch.kernel == 5)
+        rc = dispatch_stream(plan, ch.token_tile, map, prm, stream);
       else if (ch.kernel == 3)
         rc = ch.token_tile == 16 ? launch_decode<16, false>(plan, map, prm, m_tiles, ch.split_k, stream)
                                  : launch_decode<32, false>(plan, map, prm, m_tiles, ch.split_k, stream);
@@ -739,11 +863,27 @@ int sk_w2a8_plan_create(sk_w2a8_plan** out, int device, int64_t N, int64_t K, in
       }
     }
   }
+  if (rc == SK_OK && group_size == 128) {
+    // the decode kernels' copy of the scales (made once, here: later changes of w_scale_f16 are not seen by them)
+    const long long total = static_cast<long long>(plan->n_tiles) * plan->k_blocks * sk::kTileN;
+    e = cudaMalloc(&plan->w_scale_tiled, static_cast<size_t>(total) * sizeof(__half));
+    if (e != cudaSuccess) { plan->w_scale_tiled = nullptr; rc = sk::cuda_fail(plan, e); }
+    else {
+      const int blocks = static_cast<int>(total / 256 + 1 < 148 * 8 ? total / 256 + 1 : 148 * 8);
+      sk::tile_scales_kernel<<<blocks, 256>>>(plan->w_scale, plan->w_scale_tiled, N, plan->k_blocks, total);
+      e = cudaGetLastError();
+      if (e == cudaSuccess) e = cudaDeviceSynchronize();
+      if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
+    }
+  }
+  if (rc == SK_OK) rc = sk::stream_setup(plan, 0);
   if (cur >= 0 && cur != device) (void)cudaSetDevice(cur);
   if (rc != SK_OK) {
     if (plan->status) cudaFree(plan->status);
     if (plan->w_tiled_owned) cudaFree(plan->w_tiled_owned);
-
+    if (plan->stream_scratch) cudaFree(plan->stream_scratch);
+    if (plan->stream_counters) cudaFree(plan->stream_counters);
+    if (plan->w_scale_tiled) cudaFree(plan->w_scale_tiled);
     delete plan;
     return rc;
   }
@@ -758,6 +898,9 @@ int sk_w2a8_plan_destroy(sk_w2a8_plan* plan) {
   (void)cudaSetDevice(plan->device);
   if (plan->status) cudaFree(plan->status);
   if (plan->w_tiled_owned) cudaFree(plan->w_tiled_owned);
+  if (plan->stream_scratch) cudaFree(plan->stream_scratch);
+  if (plan->stream_counters) cudaFree(plan->stream_counters);
+  if (plan->w_scale_tiled) cudaFree(plan->w_scale_tiled);
   if (cur >= 0 && cur != plan->device) (void)cudaSetDevice(cur);
   delete plan;
   return SK_OK;
@@ -779,8 +922,9 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
   if (!plan) return SK_ERR_NULL_POINTER;
   switch (key) {
     case SK_OPT_KERNEL:
-      if (value < 0 || value > 4) return SK_ERR_BAD_ARGUMENT;
+      if (value < 0 || value > 5) return SK_ERR_BAD_ARGUMENT;
       if (value == 2 && !plan->w_rowmajor) return SK_ERR_UNAVAILABLE;
+      if (value == 5 && !plan->stream_scratch) return SK_ERR_UNAVAILABLE;
       if (value == 4 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       if (value == 3 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       plan->opt_kernel = static_cast<int>(value);
@@ -810,6 +954,16 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
       if (value < 0 || (value != 0 && value < 1000)) return SK_ERR_BAD_ARGUMENT;
       plan->opt_wait_limit = value;
       return SK_OK;
+    case SK_OPT_STREAM_CTAS: {
+      if (value < 0 || value > 65535) return SK_ERR_BAD_ARGUMENT;
+      if (!plan->stream_scratch) return SK_ERR_UNAVAILABLE;
+      int cur = -1;
+      cudaGetDevice(&cur);
+      (void)cudaSetDevice(plan->device);
+      const int rc = sk::stream_setup(plan, static_cast<int>(value));   // frees and allocates: orders itself after the plan's launches
+      if (cur >= 0 && cur != plan->device) (void)cudaSetDevice(cur);
+      return rc;
+    }
     case SK_OPT_TEST_SKIP_COPY:
       if (value < 0 || value > (1 << 20)) return SK_ERR_BAD_ARGUMENT;
       plan->opt_skip_copy = static_cast<int>(value);
@@ -853,6 +1007,9 @@ int sk_w2a8_last_device_status(sk_w2a8_plan* plan, int* device_status) {
   int v = 0;
   cudaError_t e = cudaMemcpy(&v, plan->status, sizeof(int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && v != 0) e = cudaMemset(plan->status, 0, sizeof(int));
+  // a launch that gave up may have left tiles of the balanced-split kernel half counted
+  if (e == cudaSuccess && v != 0 && plan->stream_counters)
+    e = cudaMemset(plan->stream_counters, 0, static_cast<size_t>(plan->n_tiles) * sk::StreamTraits<32>::kEpiWarps * sizeof(int));
   if (cur >= 0 && cur != plan->device) (void)cudaSetDevice(cur);
   if (e != cudaSuccess) return sk::cuda_fail(plan, e);
   *device_status = v;
@@ -867,7 +1024,7 @@ int sk_w2a8_launch_floor_probe(sk_w2a8_plan* plan, int64_t M, sk_stream_t stream
   sk::LaunchChoice ch;
   int rc = sk::resolve_launch(plan, M, false, &ch);
   if (rc != SK_OK) return rc;
-  if (ch.kernel != 3) return SK_ERR_UNAVAILABLE;   // the probe mirrors the decode kernel's launch
+  if (ch.kernel != 3 && ch.kernel != 5) return SK_ERR_UNAVAILABLE;   // the probe mirrors the decode kernels' launch
   int cur = -1;
   if (cudaGetDevice(&cur) != cudaSuccess) return sk::cuda_fail(plan, cudaGetLastError());
   if (cur != plan->device && cudaSetDevice(plan->device) != cudaSuccess) return sk::cuda_fail(plan, cudaGetLastError());
@@ -881,7 +1038,7 @@ int sk_w2a8_launch_floor_probe(sk_w2a8_plan* plan, int64_t M, sk_stream_t stream
   if (e == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
     const int m_tiles = static_cast<int>((M + ch.token_tile - 1) / ch.token_tile);
-    cfg.gridDim = dim3(plan->n_tiles, m_tiles, ch.split_k);
+    cfg.gridDim = ch.kernel == 5 ? dim3(plan->stream_ctas, 1, 1) : dim3(plan->n_tiles, m_tiles, ch.split_k);
     cfg.blockDim = dim3(sk::DecodeTraits<16>::kThreads, 1, 1);
     cfg.dynamicSmemBytes = dyn - 1024;
     cfg.stream = static_cast<cudaStream_t>(stream);
@@ -917,7 +1074,9 @@ const char* sk_device_status_string(int device_status) {
     case sk::kStMmaExFull: return "MMA issuer: the expanded weights of a stage never arrived";
     case sk::kStMmaAccEmpty: return "MMA issuer: an accumulator buffer was never released by the epilogue";
     case sk::kStEpilogueAccFull: return "epilogue: the MMAs of a scale group never completed";
+    case sk::kStEpilogueScales: return "epilogue: the copy of the group scales never landed";
     case sk::kStDrain: return "producer: a copy in flight did not land while the CTA was giving up";
+    case sk::kStStreamSlots: return "epilogue: a tile is shared by more CTAs than the scratch buffer has slots for";
     default: return "unknown device status";
   }
 }

@@ -40,11 +40,15 @@ struct DecodeTraits {
   static constexpr int kKbPerStage = 4;                      // K blocks per load stage
   static constexpr int kStages = TOK == 16 ? 4 : 3;
   static constexpr int kGroupsPerSet = 2;                    // scale groups (= K blocks) per accumulator set: a half stage
-  static constexpr int kAccBufs = 2 * kGroupsPerSet;         // accumulator buffers: two sets
+  // Accumulator sets.  The MMAs of half stage u + kAccSets wait until the epilogue has read half stage u, and from
+  // the commit of a half stage to the epilogue's hand-back of its set are 1500-2000 cycles (commit, barrier, two
+  // tensor-memory loads): with two sets that round trip paces the CTA, whatever the other roles do.
+  static constexpr int kAccSets = TOK == 16 ? 4 : 2;
+  static constexpr int kAccBufs = kAccSets * kGroupsPerSet;  // accumulator buffers
   static constexpr int kAccCols = kAccBufs * TOK;            // tensor memory: [0, kAccCols) accumulators, then weights
   static constexpr int kACol0 = kAccCols;
   static constexpr uint32_t kTmemCols = 256;
-  static constexpr int kASubs = (256 - kAccCols) / 64;       // half-stage buffers of expanded weights: 3 (16 tokens) or 2
+  static constexpr int kASubs = (256 - kAccCols) / 64;       // half-stage buffers of expanded weights: 2
   static constexpr int kXKbBytes = TOK * kBlockK;            // one activation box
   static constexpr int kStageWBytes = kKbPerStage * kWpBytes;
   static constexpr int kStageBytes = kStageWBytes + kKbPerStage * kXKbBytes;
@@ -54,16 +58,29 @@ struct DecodeTraits {
   // barrier before anybody pushes.
   static constexpr bool kRedInRing = (TOK == 32);
   static constexpr int kOffRed = kRedInRing ? 0 : kStages * kStageBytes;
-  static constexpr int kOffBar = kStages * kStageBytes + (kRedInRing ? 0 : TOK * kTileN * 4);
+  // The group scales of the CTA's K range (fp16 [K blocks][128 features], one bulk copy out of the plan's tiled copy
+  // of the scales): the epilogue reads its coefficients from shared memory.  Loaded from global memory one set
+  // ahead they cost it an L2 round trip per set -- about as long as everything else in a half stage.
+  // With 16 tokens the region behind the ring is [reduction buffer 8 KiB][4 KiB]: a CTA that shares its tile stages
+  // up to 16 K blocks of scales behind the reduction buffer, a CTA with a tile of its own (no reduction) up to 48 from
+  // the start of the region.  With 32 tokens (reduction buffer inside the ring) the region is 8 KiB of scales.
+  static constexpr int kRegionBytes = kRedInRing ? 32 * kTileN * 2 : TOK * kTileN * 4 + 16 * kTileN * 2;
+  static constexpr int kOffBar = kStages * kStageBytes + kRegionBytes;
+  __host__ __device__ static constexpr int scale_offset(int num_splits) {
+    return kStages * kStageBytes + ((kRedInRing || num_splits == 1) ? 0 : TOK * kTileN * 4);
+  }
+  __host__ __device__ static constexpr int scale_capacity(int num_splits) {   // in K blocks
+    return kRedInRing ? 32 : (num_splits == 1 ? kRegionBytes / (kTileN * 2) : 16);
+  }
   static_assert(TOK * kTileN * 4 <= kStages * kStageBytes, "reduction buffer");
   static constexpr int kSubRing = 2 * kStages;               // ring of "MMAs of a half stage are complete" barriers
-  static constexpr int kNumBars = kStages + kSubRing + kASubs + 2;
+  static constexpr int kNumBars = kStages + kSubRing + kASubs + kAccSets + 1;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kTotal = kOffMisc + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;        // slack for 1024-byte alignment of the base
   static constexpr int kEpiWarps = 4, kExpWarps = 4;
   static constexpr int kThreads = 384;                       // 4 epilogue + 4 expander + producer + 2 MMA warps, + 1 idle
-  static_assert(2 * kDynamicBytes <= 227 * 1024, "two CTAs per SM");
+  static_assert(2 * (kDynamicBytes + 1024) <= 228 * 1024, "two CTAs per SM (1 KiB per CTA is reserved by the system)");
 };
 
 template <int TOK, bool DUMP>
@@ -87,7 +104,8 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   // decode-sized tile, so they are the currency to save.
   const uint32_t bar_sub_done = bar_ld_full + 8u * S;
   const uint32_t bar_ex_full = bar_sub_done + 8u * T::kSubRing;   // [kASubs] expanded weights of a half stage are in tensor memory
-  const uint32_t bar_acc_empty = bar_ex_full + 8u * T::kASubs;    // [2] the epilogue has read the accumulator set
+  const uint32_t bar_acc_empty = bar_ex_full + 8u * T::kASubs;    // [kAccSets] the epilogue has read the accumulator set
+  const uint32_t bar_scale = bar_acc_empty + 8u * T::kAccSets;    // the group scales of the K range have landed
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + T::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + T::kOffMisc + 4);
   const WaitCtx ctx{abort_flag, p.status, p.wait_limit};
@@ -105,6 +123,8 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   const int kb_begin = min(split * per_split, p.groups);
   const int nkb = min(kb_begin + per_split, p.groups) - kb_begin;
   const uint32_t bias = 1u << 22;
+  const bool scales_staged = p.w_scale_tiled != nullptr && nkb <= T::scale_capacity(num_splits) && nkb > 0;
+  const int off_scale = T::scale_offset(num_splits);
 
   // ---------------------------------------------------------------- set-up
   if (threadIdx.x == 0) SK_TRACE_EVENT(4, 0);
@@ -116,7 +136,13 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
   grid_dep_launch_dependents();
   if (warp == kProducerWarp && lane == 0) {
     for (int i = 0; i < S; ++i) mbar_init(bar_ld_full + 8 * i, 1);
+    mbar_init(bar_scale, 1);
     fence_mbar_init();
+    if (scales_staged) {
+      mbar_arrive_expect_tx(bar_scale, static_cast<uint32_t>(nkb) * (kTileN * 2));
+      bulk_load_1d(smem_base + off_scale, p.w_scale_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kTileN,
+                   static_cast<uint32_t>(nkb) * (kTileN * 2), bar_scale);
+    }
     const uint8_t* w = p.w_tiled + (static_cast<size_t>(n_tile) * p.k_blocks + kb_begin) * kWpBytes;
     for (int i = 0, st = 0; i < nkb && st < S; i += T::kKbPerStage, ++st) {
       const int n = min(T::kKbPerStage, nkb - i);
@@ -130,7 +156,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     }
     for (int i = 0; i < T::kSubRing; ++i) mbar_init(bar_sub_done + 8 * i, 1);
     for (int i = 0; i < T::kASubs; ++i) mbar_init(bar_ex_full + 8 * i, T::kExpWarps);
-    for (int i = 0; i < 2; ++i) mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps);
+    for (int i = 0; i < T::kAccSets; ++i) mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmap_x);
@@ -220,7 +246,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       const int a = u % T::kASubs;              // tensor-memory buffer of expanded weights
       ok = wait_bounded(bar_ld_full + 8 * stage, (q / S) & 1, ctx, kStMmaLdFull) &&
            wait_bounded(bar_ex_full + 8 * a, (u / T::kASubs) & 1, ctx, kStMmaExFull) &&
-           wait_bounded(bar_acc_empty + 8 * (u & 1), (u >> 1) & 1, ctx, kStMmaAccEmpty);
+           wait_bounded(bar_acc_empty + 8 * (u % T::kAccSets), (u / T::kAccSets) & 1, ctx, kStMmaAccEmpty);
       if (!ok) break;
       tcgen05_fence_after_sync();
       if (elect_one()) {
@@ -305,13 +331,21 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     tmem_st_wait();
     tcgen05_fence_before_sync();
     __syncwarp();
-    if (lane == 0) { mbar_arrive(bar_acc_empty); mbar_arrive(bar_acc_empty + 8); }
+    if (lane == 0)
+      for (int i = 0; i < T::kAccSets; ++i) mbar_arrive(bar_acc_empty + 8 * i);
 
     // group scales: coefficient of group i is (s_i - s_{i + kAccBufs}) * 2^100 (s = 0 past the end of the range);
     // the coefficients of a set are fetched one set ahead, and the rows behind them pulled into L2 earlier still
     const unsigned short* sp =
         reinterpret_cast<const unsigned short*>(p.w_scale) + static_cast<size_t>(kb_begin) * p.N + (n_ok ? n : 0);
+    const uint32_t scale_smem = smem_base + off_scale + row * 2;
     auto scale_at = [&](int g) -> float {
+      if (scales_staged) {   // (rows past N are zero in the tiled copy)
+        if (g >= nkb) return 0.f;
+        unsigned short h;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(scale_smem + g * (kTileN * 2)));
+        return __half2float(__ushort_as_half(h));
+      }
       return (n_ok && g < nkb) ? __half2float(__ushort_as_half(__ldg(sp + static_cast<size_t>(g) * p.N))) : 0.f;
     };
     auto coeffs = [&](int si, float (&c)[GS]) {
@@ -320,11 +354,11 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       const int ahead = (si + 3) * GS + T::kAccBufs;      // first row the set after next will need
 #pragma unroll
       for (int j = 0; j < GS; ++j)
-        if (ahead + j < nkb) asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + static_cast<size_t>(ahead + j) * p.N));
+        if (!scales_staged && ahead + j < nkb) asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + static_cast<size_t>(ahead + j) * p.N));
     };
     if (!DUMP && warp == 0 && lane < TOK && m0 + lane < p.M)   // the token scales are read at the very end: have them in L2 by then
       asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x_scale + m0 + lane));
-    {   // rows the first sets need: pull this warp's 64-byte segment of each into L2 now
+    if (!scales_staged) {   // rows the first sets need: pull this warp's 64-byte segment of each into L2 now
       const int seg = min(n0 + warp * 32, p.N - 1);
       const unsigned short* base = reinterpret_cast<const unsigned short*>(p.w_scale) + static_cast<size_t>(kb_begin) * p.N + seg;
       for (int g = lane; g < min(nkb, 3 * GS + T::kAccBufs); g += 32)
@@ -335,13 +369,14 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 #pragma unroll
     for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
     float c_cur[GS], c_next[GS];
+    bool ok = true;
+    if (scales_staged) ok = wait_bounded(bar_scale, 0, ctx, kStEpilogueScales);
     coeffs(0, c_cur);
     grid_dep_wait();   // nothing completes before the activations exist: do not poll next to the running kernel
     float s_sum = 0.f;
     int flush = 0;
-    bool ok = true;
     const int num_sets = (nkb + GS - 1) / GS;
-    for (int si = 0; si < num_sets; ++si) {
+    for (int si = 0; si < num_sets && ok; ++si) {
       coeffs(si + 1, c_next);      // zeros past the end
       // set si is complete when the MMAs of half stage si are
       ok = wait_bounded(bar_sub_done + 8 * (si % T::kSubRing), (si / T::kSubRing) & 1, ctx, kStEpilogueAccFull);
@@ -351,13 +386,13 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 #pragma unroll
       for (int j = 0; j < GS; ++j) {
         uint32_t v[TOK];
-        if constexpr (TOK == 16) tmem_ld_32x16(lane_addr + (si & 1) * (GS * TOK) + j * TOK, v);
-        else tmem_ld_32x32(lane_addr + (si & 1) * (GS * TOK) + j * TOK, v);
+        if constexpr (TOK == 16) tmem_ld_32x16(lane_addr + (si % T::kAccSets) * (GS * TOK) + j * TOK, v);
+        else tmem_ld_32x32(lane_addr + (si % T::kAccSets) * (GS * TOK) + j * TOK, v);
         tmem_ld_wait();
         if (j == GS - 1) {
           tcgen05_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * (si & 1));   // the MMAs keep accumulating into the set
+          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * (si % T::kAccSets));   // the MMAs keep accumulating into the set
         }
         if constexpr (DUMP) {
           const int g = si * GS + j;

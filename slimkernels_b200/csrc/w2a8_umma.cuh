@@ -58,15 +58,19 @@ enum : int {
   kStProducerEmpty = 0x11,
   kStExpanderFull = 0x21, kStExpanderEmpty = 0x22,
   kStMmaLdFull = 0x31, kStMmaExFull = 0x32, kStMmaAccEmpty = 0x33,
-  kStEpilogueAccFull = 0x41,
-  kStDrain = 0x51
+  kStEpilogueAccFull = 0x41, kStEpilogueScales = 0x42,
+  kStDrain = 0x51,
+  kStStreamSlots = 0x61   // balanced-split decode kernel: host and device disagree on how a tile is cut (never expected)
 };
 
 // Optional in-kernel timeline (compiled only with -DSK_TRACE): CTA (0,0,0) stores SM clock stamps.
 #ifdef SK_TRACE
+#ifndef SK_TRACE_CTA
+#define SK_TRACE_CTA 0
+#endif
 #define SK_TRACE_EVENT(role, idx)                                                                 \
   do {                                                                                            \
-    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 64)           \
+    if (p.trace && blockIdx.x == SK_TRACE_CTA && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 64) \
       p.trace[(role) * 64 + (idx)] = clock64();                                                   \
   } while (0)
 #define SK_TRACE_BASE (((tile - tile_first) / tile_step) * (kb_end - kb_begin))   /* events of earlier tiles */
@@ -81,6 +85,7 @@ struct ExtraOutMaps { CUtensorMap map[7]; };
 struct GemmParams {
   const uint8_t* w_tiled;     // [n_tiles][k_blocks][4096]
   const __half* w_scale;      // [groups, N]
+  const __half* w_scale_tiled;  // [n_tiles][k_blocks][128] copy of w_scale (group size 128; rows past N zero), or nullptr
   const float* x_scale;       // [M]
   void* out;                  // [M, ld_out] half or bf16
   void* out_extra[7];         // further destinations of the same tile (peer GPUs' buffers), same ld_out
@@ -100,6 +105,10 @@ struct GemmParams {
   long long wait_limit;       // SM cycles after which a wait inside the kernel gives up (kWaitLimitCycles by default)
   int fault_skip_kb;          // failure-path test hook: the producer leaves out the copies of this K block of its
                               // range (-1: off), so that the waits for them run into the limit
+  // balanced-split decode kernel (w2a8_stream.cuh): partial sums of tiles shared between CTAs
+  float* stream_scratch;      // [n_tiles][stream_slots][token tile][128] fp32
+  int* stream_counters;       // [n_tiles][4]: contributions received per (tile, epilogue warp); zero between launches
+  int stream_slots;           // slots per tile = the most CTAs that can share one tile
 #ifdef SK_TRACE
   long long* trace;           // [8][64] clock stamps of CTA (0,0,0)
 #endif

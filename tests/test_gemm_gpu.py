@@ -91,6 +91,73 @@ def test_decode_kernel_every_tile_split_and_depth(token_tile, split_k, K):
     _check(prob, force=dict(kernel=capi.KERNEL_TCGEN05_DECODE, token_tile=token_tile, split_k=split_k))
 
 
+@pytest.mark.parametrize("M,N,K,ctas", [
+    (1, 128, 256, 0),        # one tile, one half stage: a single CTA writes it out directly
+    (13, 392, 1024, 0),      # ragged M and N; every CTA one half stage
+    (16, 392, 4096, 5),      # ranges of 12.8 half stages: tiles shared by two and three CTAs, cuts inside tiles
+    (7, 1000, 2048, 3),      # ranges longer than a tile: direct tiles and shared tiles in one CTA
+    (16, 640, 8192, 37),     # uneven cut of 160 half stages
+    (29, 392, 1408 + 128, 4),  # 32-token tile, K = 12 K blocks
+    (32, 1280, 4096, 296),   # more CTAs asked for than half stages exist: clamped
+])
+def test_balanced_split_decode_kernel(M, N, K, ctas):
+    """The decode kernel that cuts the K range of the whole problem into equal CTA ranges: partial sums of shared
+    tiles meet in the plan's scratch buffer and are added in slot order, so repeated launches are bit-identical."""
+    x_q, xs, wp, ws = random_problem(M, N, K, 128, seed=M + N + K)
+    dp = DeviceProblem(x_q, xs, wp, ws).force(kernel=capi.KERNEL_TCGEN05_DECODE_BALANCED)
+    if ctas:
+        dp.plan.set_option(capi.SK_OPT_STREAM_CTAS, ctas)
+    q = dp.plan.query_launch(M)
+    assert q["kernel"] == capi.KERNEL_TCGEN05_DECODE_BALANCED and q["split_k"] == 1
+    assert q["ctas"] == min(ctas or 2 * torch.cuda.get_device_properties(0).multi_processor_count, (N + 127) // 128 * (K // 256))
+    y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)
+    y = [dp.gemm() for _ in range(3)]
+    assert np.abs(to_np(y[0]) - y_ref).max() <= TOL
+    assert torch.equal(y[0], y[1]) and torch.equal(y[0], y[2])
+    # against the kernel that splits over clusters: same arithmetic up to the order of the fp32 partial sums
+    y_cluster = dp.force(kernel=capi.KERNEL_TCGEN05_DECODE, split_k=1).gemm()
+    assert np.abs(to_np(y[0]) - to_np(y_cluster)).max() <= 4e-3 * max(1.0, float(np.abs(y_ref).max()))
+    # debug partials of a plan forced to the balanced kernel come from the cluster kernel: bit-exact
+    dp.force(kernel=capi.KERNEL_TCGEN05_DECODE_BALANCED)
+    np.testing.assert_array_equal(to_np(dp.partials()), O.w2a8_partials(x_q, wp, 128))
+
+
+def test_balanced_split_kernel_falls_back_where_it_does_not_apply():
+    # K = 5 K blocks (odd): no whole half stages; several token tiles; a forced split
+    x_q, xs, wp, ws = random_problem(8, 256, 640, 128, seed=11)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    with pytest.raises(capi.SkError):
+        dp.plan.set_option(capi.SK_OPT_KERNEL, capi.KERNEL_TCGEN05_DECODE_BALANCED)   # the plan has no scratch buffer
+    x_q, xs, wp, ws = random_problem(40, 256, 1024, 128, seed=12)
+    dp = DeviceProblem(x_q, xs, wp, ws).force(kernel=capi.KERNEL_TCGEN05_DECODE_BALANCED, token_tile=16)
+    assert dp.plan.query_launch(40)["kernel"] == capi.KERNEL_TCGEN05_DECODE      # three token tiles
+    assert np.abs(to_np(dp.gemm()) - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+    dp.force(kernel=capi.KERNEL_TCGEN05_DECODE_BALANCED, split_k=2)
+    assert dp.plan.query_launch(8)["kernel"] == capi.KERNEL_TCGEN05_DECODE
+    # group size 64: general kernel
+    x_q, xs, wp, ws = random_problem(8, 256, 1024, 64, seed=13)
+    dp = DeviceProblem(x_q, xs, wp, ws, group_size=64)
+    with pytest.raises(capi.SkError):
+        dp.plan.set_option(capi.SK_OPT_KERNEL, capi.KERNEL_TCGEN05_DECODE_BALANCED)
+
+
+def test_balanced_split_is_the_default_for_large_decode_problems():
+    """From 64 K blocks per SM on (16-token tile) the balanced split is the default; 32-token tiles stay with clusters."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    N = 448 * 128
+    for K in (2048, 4096):      # 48 and 97 K blocks per SM on 148 SMs
+        x_q, xs, wp, ws = random_problem(16, N, K, 128, seed=K)
+        dp = DeviceProblem(x_q, xs, wp, ws)
+        big = (N // 128) * (K // 128) >= 64 * sms
+        want = capi.KERNEL_TCGEN05_DECODE_BALANCED if big else capi.KERNEL_TCGEN05_DECODE
+        assert dp.plan.query_launch(16)["kernel"] == want
+        assert dp.plan.query_launch(32)["kernel"] == capi.KERNEL_TCGEN05_DECODE
+        y = to_np(dp.gemm())
+        cols = np.arange(0, N, 997)
+        y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp[cols], ws[:, cols])
+        assert np.abs(y[:, cols] - y_ref).max() <= TOL
+
+
 def test_decode_kernel_is_the_default_for_small_batches():
     x_q, xs, wp, ws = random_problem(8, 512, 2048, 128, seed=3)
     dp = DeviceProblem(x_q, xs, wp, ws)
