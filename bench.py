@@ -203,14 +203,17 @@ def time_events(fn, iters, stream):
 
 
 def decode_sweep(dev, peaks):
-    """Llama-2-7B decode shapes: CUDA graph of 64 GEMMs cycling weight copies that total > 2x L2."""
+    """Llama-2-7B decode shapes (and the two Llama-3-70B MLP projections at decode size): CUDA graph of 64 GEMMs
+    cycling weight copies that total > 2x L2."""
     import torch
     from slimkernels_b200 import workloads as W
     from slimkernels_b200.torch import W2A8Plan
     l2 = torch.cuda.get_device_properties(dev).L2_cache_size
     out = []
     rng = np.random.default_rng(0)
-    for name, (N, K) in W.LLAMA2_7B_SHAPES.items():
+    shapes = dict(W.LLAMA2_7B_SHAPES)
+    shapes.update({"llama3_70b_gate_up": (57344, 8192), "llama3_70b_down": (8192, 28672)})
+    for name, (N, K) in shapes.items():
         G = 128
         wbytes = N * K // 4 + (K // G) * N * 2
         ncopies = min(64, max(2, int(np.ceil(2.0 * l2 / wbytes)) + 1))
@@ -259,7 +262,7 @@ def decode_sweep(dev, peaks):
             us_floor = ms_floor * 1e3
             gbs = wbytes / (ms_graph * 1e-3) / 1e9
             stream_us = wbytes / (peaks["hbm_gbs"] * 1e9) * 1e6
-            q = plans[0].query_launch(M)
+            desc, q = kernel_description(plans[0], M)
             out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(us, 3), "gbs": round(gbs, 1),
                         "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "us_single_launch_l2_warm": round(ms_single * 1e3, 3),
                         "us_launch_floor": round(us_floor, 3),
@@ -267,8 +270,7 @@ def decode_sweep(dev, peaks):
                         "gbs_above_floor": round(wbytes / max(us - us_floor, 1e-3) / 1e3, 1),
                         "frac_hbm_ceiling_floor_plus_streaming": round(stream_us / (us_floor + stream_us), 4),
                         "weight_copies": ncopies, "algorithmic_bytes": wbytes,
-                        "kernel": "w2a8_decode_kernel (tcgen05.mma kind::i8, weights expanded into tensor memory): "
-                                  f"token tile {q['token_tile']}, split-K {q['split_k']}, {q['ctas']} CTAs"})
+                        "kernel": desc})
         del plans
         torch.cuda.empty_cache()
     return out
@@ -428,7 +430,9 @@ def kernel_description(plan, M):
     q = plan.query_launch(M)
     kind = {1: "w2a8_umma_kernel (tcgen05.mma kind::i8, weights expanded to int8 in shared memory)",
             2: "w2a8_simt_kernel (CUDA cores)",
-            3: "w2a8_decode_kernel (tcgen05.mma kind::i8, weights expanded into tensor memory)",
+            3: "w2a8_decode_kernel (tcgen05.mma kind::i8, weights expanded into tensor memory, split-K over a cluster)",
+            5: "w2a8_stream_kernel (tcgen05.mma kind::i8, weights expanded into tensor memory, K range of the whole "
+               "problem cut into equal CTA ranges)",
             4: "w2a8_pair_kernel (tcgen05.mma cta_group::2 kind::i8, two CTAs share one token tile)"}.get(q["kernel"], "?")
     return f"{kind}: token tile {q['token_tile']}, split-K {q['split_k']}, {q['ctas']} CTAs", q
 

@@ -121,8 +121,11 @@ int sk_w2a8_gemm(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,
 /* The same GEMM, written to several destinations at once: the [M, N] result lands at column `col_offset` of each
  * of the n_outs (1..8) row-major buffers outs[i] of leading dimension ld_out.  outs[0] is a local buffer, the
  * others may be peer-mapped buffers of other GPUs (CUDA IPC / symmetric memory): the kernel's epilogue stores
- * every tile to all of them with plain global stores, so an N-sharded all-gather of the output overlaps the
- * GEMM.  The caller synchronises the ranks afterwards.  No counterpart in the reference (single-GPU only). */
+ * every finished tile to all of them, so an N-sharded all-gather of the output overlaps the GEMM.  Where every
+ * destination is 16-byte aligned, ld_out % 8 == 0 and N % 8 == 0 a tile leaves as one TMA store per destination
+ * (stores only: nothing is ever loaded from a peer, and no multicast is used); otherwise the epilogue threads
+ * store 16-byte vectors or single elements.  The caller synchronises the ranks afterwards.  No counterpart in the
+ * reference (single-GPU only). */
 int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
                          void* const* outs, int n_outs, int64_t ld_out, int64_t col_offset, sk_stream_t stream);
 

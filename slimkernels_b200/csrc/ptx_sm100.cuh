@@ -83,7 +83,8 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
                : "memory");
 }
-// ---------------------------------------------------------------- TMA stores (shared -> this GPU's global memory)
+// ---------------------------------------------------------------- TMA stores (shared -> global memory: this GPU's, or a
+// peer GPU's output buffer mapped into this process -- stores to peers are allowed, loads from peers are never issued)
 // x * element size must be a multiple of 16 bytes; rows / columns outside the tensor are not written.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"

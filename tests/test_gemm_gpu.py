@@ -254,7 +254,8 @@ def test_wider_output_buffer_and_padded_activation_rows():
 
 @pytest.mark.parametrize("zp", [0, 3])
 def test_other_zero_points(zp):
-    """Zero points 0 and 3 reach |code - zp| = 3, which switches the accumulator bias to 2^16."""
+    """Zero points 0 and 3 reach |code - zp| = 3: the largest per-group sums (128 * 127 * 3) and the tightest depth bound
+    of the int32 running sums under the accumulator bias 2^22."""
     _check(random_problem(20, 256, 512, 128, seed=zp), zp=zp)
 
 
