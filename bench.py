@@ -490,6 +490,72 @@ def parity_check(y_full, x_q_np, x_scale_np, wl, world, rank, seed, plan_cls, de
             "partials_checked": f"[{K // G} groups, {mt} tokens, features {rank * n_local + t0}..+128]"}
 
 
+def measure_k_sharded(wl, seed, args, dev, world, rank, steps):
+    """The down projection split along K (the layout a tensor-parallel MLP block needs behind an N-sharded gate+up):
+    every rank multiplies its K slice, the partial sums are reduce-scattered by token rows.  Device-timed step (max
+    over ranks) for the fused exchange (peer stores from the GEMM's epilogue) and for NCCL all-to-all after the GEMM;
+    the two must agree bit for bit, and sampled columns of rank 0's rows are checked against the CPU oracle."""
+    import torch
+    import torch.distributed as dist
+    from oracle import w2a8_oracle as O
+    from slimkernels_b200.torch.sharded import KShardedW2A8Gemm
+    M, N, K, G = wl["M"], wl["N"], wl["K"], wl["G"]
+    per = K // world
+    rows = M // world
+    if K % (world * G) or M % world or rows % 256:
+        return {"skipped": f"K={K} / M={M} do not split over {world} ranks in whole groups and 256-token tiles"}
+
+    def k_slice(r):       # every rank can re-draw any rank's slice on the host (for the check)
+        rng = np.random.default_rng([seed, 77, r])
+        return (rng.integers(0, 256, size=(N, per // 4), dtype=np.uint8),
+                rng.uniform(0.001, 0.01, size=(per // G, N)).astype(np.float16),
+                rng.integers(-127, 128, size=(M, per), dtype=np.int8),
+                rng.uniform(0.005, 0.02, size=(M,)).astype(np.float32))
+
+    wp_np, ws_np, xq_np, xs_np = k_slice(rank)
+    wp, ws = torch.from_numpy(wp_np).to(dev), torch.from_numpy(ws_np).to(dev)
+    d_x, d_xs = torch.from_numpy(xq_np).to(dev), torch.from_numpy(xs_np).to(dev)
+    stream = torch.cuda.current_stream(dev)
+    out = {"workload": wl["name"] + "_k_sharded", "M": M, "N": N, "K": K, "rows_per_rank": rows,
+           "bytes_sent_per_rank": (world - 1) * rows * N * 2}
+    results = {}
+    for fused in (True, False):
+        op = KShardedW2A8Gemm(wp, ws, group_size=G, fused=fused)
+        for _ in range(3):
+            y = op(d_x, d_xs)
+        dist.barrier(); torch.cuda.synchronize(dev)
+        ms = time_events(lambda: op(d_x, d_xs), steps, stream)
+        dist.barrier(); torch.cuda.synchronize(dev)
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        results[fused] = op(d_x, d_xs).clone()
+        out["fused_peer_stores" if fused else "nccl_all_to_all"] = {
+            "ms_per_step": round(ms, 4), "tops": round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 2)}
+        del op
+    same = torch.tensor([1 if torch.equal(results[True], results[False]) else 0], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    out["fused_equals_nccl_bitwise"] = bool(same.item())
+    ok = True
+    if rank == 0:
+        cols = np.sort(np.random.default_rng([seed, 4321]).choice(N, size=32, replace=False))
+        ref = np.zeros((rows, len(cols)), dtype=np.float32)
+        for r in range(world):
+            wp_r, ws_r, xq_r, xs_r = k_slice(r)
+            ref += O.w2a8_gemm_dequant_path(xq_r[:rows], xs_r[:rows], np.ascontiguousarray(wp_r[cols]),
+                                            np.ascontiguousarray(ws_r[:, cols]), G).astype(np.float32)
+        err = float(np.abs(results[True].float().cpu().numpy()[:, cols] - ref).max())
+        out["parity"] = {"max_abs_err": round(err, 6), "tol": 1e-2, "cols_checked": int(len(cols)), "rows_checked": rows,
+                         "ok": bool(err <= 1e-2 and out["fused_equals_nccl_bitwise"])}
+        ok = out["parity"]["ok"]
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, 0)
+    out["_ok"] = bool(flag.item())
+    del wp, ws, d_x, d_xs, results
+    torch.cuda.empty_cache()
+    return out
+
+
 def measure_workload(wl, seed, args, dev, world, rank, fused, steps, peaks, with_e2e=False, with_parity=True):
     """One N-sharded GEMM (+ exchange) workload: device-timed step (max over ranks), this rank's GEMM alone (warmed,
     min / median / max over ranks), exchange figures, parity.  Returns a dict (same on every rank)."""
@@ -680,7 +746,9 @@ def run_ours(args):
     def strip(d):
         return {k: v for k, v in d.items() if not k.startswith("_")}
 
-    # ---- the other GEMM of benchmark config 3 (down projection, N-sharded the same way) and the other exchange
+    # ---- the other GEMM of benchmark config 3 (down projection, N-sharded the same way), the other exchange, and
+    # the down projection split along K with the reduce-scatter fused into the GEMM's epilogue
+    k_sharded_ok = True
     if not args.no_sweeps or world > 1:
         few = max(3, min(args.steps, 10))
         extra = {}
@@ -688,6 +756,9 @@ def run_ours(args):
         if world > 1:
             extra["gate_up_other_exchange"] = strip(measure_workload(WORKLOAD, 0, args, dev, world, rank, not fused, few, peaks))
             extra["down_proj_other_exchange"] = strip(measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, not fused, few, peaks))
+            ks = measure_k_sharded(WORKLOAD_DOWN, 2, args, dev, world, rank, few)
+            k_sharded_ok = ks.pop("_ok", True)
+            extra["down_proj_k_sharded"] = ks
         line["config3"] = extra
 
     if world == 1 and not args.no_sweeps:
@@ -699,7 +770,8 @@ def run_ours(args):
         line["mlp_block"] = mlp_block_sweep(dev, peaks)
     if world == 1 and rank == 0:
         line["cpu_baseline"] = run_cpu_baseline()
-    ok = line["parity"]["ok"] and all(v.get("parity", {"ok": True})["ok"] for v in line.get("config3", {}).values())
+    ok = line["parity"]["ok"] and k_sharded_ok and \
+        all(v.get("parity", {"ok": True})["ok"] for v in line.get("config3", {}).values())
     line["parity_all_ok"] = bool(ok)
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -129,6 +129,19 @@ int sk_w2a8_gemm(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,
 int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
                          void* const* outs, int n_outs, int64_t ld_out, int64_t col_offset, sk_stream_t stream);
 
+/* The same GEMM with its token rows dealt out: rows [d * rows_per_dest, (d + 1) * rows_per_dest) of the [M, N]
+ * result go to destination outs[d] ONLY (n_outs = 1..8, M == n_outs * rows_per_dest), where they land at rows
+ * dst_row0 .. dst_row0 + rows_per_dest - 1 of a row-major buffer of leading dimension ld_out.  This is the
+ * scatter half of a reduce-scatter: with the weight split along K over R ranks, rank r calls it with
+ * outs[d] = rank d's [R * rows_per_dest, N] buffer (peer-mapped for d != r) and dst_row0 = r * rows_per_dest, so that
+ * after a barrier rank d holds the R partial sums of its rows, block r from rank r, and adds them in rank order.
+ * Stores only (TMA stores of whole tiles where alignment allows, as for sk_w2a8_gemm_scatter); nothing is loaded
+ * from a peer.  rows_per_dest must be a multiple of the token tile the plan uses for M (256 for M > 128), and the
+ * launch must be the general kernel's: SK_ERR_UNAVAILABLE otherwise.  No counterpart in the reference. */
+int sk_w2a8_gemm_rowscatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
+                            void* const* outs, int n_outs, int64_t rows_per_dest, int64_t dst_row0, int64_t ld_out,
+                            sk_stream_t stream);
+
 /* Same contraction, but stores the exact per-group integer partial sums
  * partials[g, m, n] (int32, [K/G, M, N] contiguous) instead of the scaled output. */
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,

@@ -42,6 +42,7 @@ SIGNATURES = {
                                  ctypes.POINTER(_int), ctypes.POINTER(_int), ctypes.POINTER(_int)]),
     "sk_w2a8_gemm": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp]),
     "sk_w2a8_gemm_scatter": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.POINTER(_vp), _int, _i64, _i64, _vp]),
+    "sk_w2a8_gemm_rowscatter": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.POINTER(_vp), _int, _i64, _i64, _i64, _vp]),
     "sk_w2a8_gemm_debug_partials": (_int, [_vp, _i64, _vp, _i64, _vp, _vp]),
     "sk_quantize_activation_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "sk_silu_mul_quantize_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),

@@ -612,7 +612,8 @@ static int get_out_map(sk_w2a8_plan* plan, const void* out, long long M, long lo
 
 static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long long ld_x, const float* x_scale,
                     void* out, long long ld_out, int32_t* partials, cudaStream_t stream,
-                    void* const* extra_outs = nullptr, int n_extra = 0) {
+                    void* const* extra_outs = nullptr, int n_extra = 0, long long scatter_rows = 0,
+                    long long scatter_row0 = 0) {
   if (!plan || !x_q) return SK_ERR_NULL_POINTER;
   if (!partials && (!x_scale || !out)) return SK_ERR_NULL_POINTER;
   if (M <= 0 || M > 0x7fffffffLL / 2) return SK_ERR_BAD_SHAPE;
@@ -633,6 +634,11 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
   if (rc != SK_OK) {
     if (cur != plan->device) (void)cudaSetDevice(cur);
     return rc;
+  }
+  if (scatter_rows > 0 && (ch.kernel != 1 || ch.split_k != 1 || (scatter_rows % ch.token_tile) != 0)) {
+    // row scatter is the general kernel's: every token tile must belong to one destination
+    if (cur != plan->device) (void)cudaSetDevice(cur);
+    return SK_ERR_UNAVAILABLE;
   }
   if (ch.kernel == 2) {
     if (!plan->w_rowmajor || n_extra > 0) rc = SK_ERR_UNAVAILABLE;
@@ -657,6 +663,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.x_scale = x_scale;
       prm.out = out;
       prm.n_extra = n_extra;
+      prm.scatter_rows = static_cast<int>(scatter_rows);
+      prm.scatter_row0 = static_cast<int>(scatter_row0);
       for (int i = 0; i < 7; ++i) prm.out_extra[i] = i < n_extra ? extra_outs[i] : nullptr;
       prm.partials = partials;
       prm.status = plan->status;
@@ -683,7 +691,7 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       // The persistent kernel stores through TMA (and 16-byte vectors for further destinations): the output must be
       // 16-byte aligned with a pitch that is a multiple of 8 elements, N a multiple of 8 (the tensor map's extent in
       // bytes), and with further destinations the feature tiles must be whole.
-      bool persist = ch.persistent && !partials && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
+      bool persist = ch.persistent && scatter_rows == 0 && !partials && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
                      (reinterpret_cast<uintptr_t>(out) & 15) == 0;
       if (persist && n_extra > 0) {
         if (plan->N % 128) persist = false;
@@ -702,10 +710,12 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.tma_out = 0;
       if (!persist && !partials && (ch.kernel == 1 || ch.kernel == 4) && ch.split_k == 1 && (ld_out % 8) == 0 && (plan->N % 8) == 0 &&
           (reinterpret_cast<uintptr_t>(out) & 15) == 0 && plan->opt_tma_store != 1) {
-        bool ok = get_out_map(plan, out, M, ld_out, ch.token_tile, &out_map) == SK_OK;
+        // (row scatter: a destination holds scatter_row0 + scatter_rows rows at least; its map is clipped there)
+        const long long map_rows = scatter_rows > 0 ? scatter_row0 + scatter_rows : M;
+        bool ok = get_out_map(plan, out, map_rows, ld_out, ch.token_tile, &out_map) == SK_OK;
         for (int i = 0; ok && i < n_extra; ++i)
           ok = (reinterpret_cast<uintptr_t>(extra_outs[i]) & 15) == 0 &&
-               get_out_map(plan, extra_outs[i], M, ld_out, ch.token_tile, &extra_maps.map[i]) == SK_OK;
+               get_out_map(plan, extra_outs[i], map_rows, ld_out, ch.token_tile, &extra_maps.map[i]) == SK_OK;
         prm.tma_out = ok ? 1 : 0;
       }
       if (m_tiles > 65535) rc = SK_ERR_BAD_SHAPE;
@@ -991,6 +1001,20 @@ int sk_w2a8_gemm_scatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64
   }
   return sk::run_gemm(plan, M, x_q, ld_x, x_scale, shifted[0], ld_out, nullptr, static_cast<cudaStream_t>(stream),
                       shifted + 1, n_outs - 1);
+}
+
+int sk_w2a8_gemm_rowscatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, const float* x_scale,
+                            void* const* outs, int n_outs, int64_t rows_per_dest, int64_t dst_row0, int64_t ld_out,
+                            sk_stream_t stream) {
+  if (!outs) return SK_ERR_NULL_POINTER;
+  if (n_outs < 1 || n_outs > 8) return SK_ERR_BAD_ARGUMENT;
+  if (!plan) return SK_ERR_NULL_POINTER;
+  if (rows_per_dest <= 0 || dst_row0 < 0 || M != rows_per_dest * n_outs) return SK_ERR_BAD_SHAPE;
+  if (dst_row0 + rows_per_dest > 0x7fffffffLL) return SK_ERR_BAD_SHAPE;
+  for (int i = 0; i < n_outs; ++i)
+    if (!outs[i]) return SK_ERR_NULL_POINTER;
+  return sk::run_gemm(plan, M, x_q, ld_x, x_scale, outs[0], ld_out, nullptr, static_cast<cudaStream_t>(stream),
+                      outs + 1, n_outs - 1, rows_per_dest, dst_row0);
 }
 
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x, int32_t* partials,

@@ -96,6 +96,25 @@ void gemm_scatter(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_sca
         "w2a8_gemm_scatter");
 }
 
+// outs[d]: raw device pointer of rank d's [n_outs * rows_per_dest, ld_out] buffer (peer-mapped unless it is this rank's)
+void gemm_rowscatter(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, std::vector<int64_t> out_ptrs,
+                     int64_t rows_per_dest, int64_t dst_row0, int64_t ld_out, int64_t K) {
+  check_x(x_q, K);
+  const int64_t M = x_q.size(0);
+  TORCH_CHECK(x_scale.is_cuda() && x_scale.scalar_type() == at::kFloat && x_scale.is_contiguous() &&
+                  x_scale.numel() == M, "x_scale must be contiguous float32 [M]");
+  TORCH_CHECK(!out_ptrs.empty() && out_ptrs.size() <= 8, "1..8 destinations");
+  TORCH_CHECK(M > 0, "no tokens");
+  std::vector<void*> ptrs;
+  for (int64_t v : out_ptrs) ptrs.push_back(reinterpret_cast<void*>(static_cast<intptr_t>(v)));
+  c10::cuda::CUDAGuard guard(x_q.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check(sk_w2a8_gemm_rowscatter(as_plan(handle), M, x_q.data_ptr<int8_t>(), x_q.stride(0), x_scale.data_ptr<float>(),
+                                ptrs.data(), static_cast<int>(ptrs.size()), rows_per_dest, dst_row0, ld_out,
+                                stream.stream()),
+        "w2a8_gemm_rowscatter");
+}
+
 at::Tensor gemm(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, int64_t N, int64_t K, bool bf16_out) {
   at::Tensor out = at::empty({x_q.size(0), N}, x_q.options().dtype(bf16_out ? at::kBFloat16 : at::kHalf));
   gemm_out(handle, x_q, x_scale, out, K);
@@ -306,6 +325,7 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_gemm(int plan, Tensor x_q, Tensor x_scale, int N, int K, bool bf16_out) -> Tensor", &gemm);
   m.def("w2a8_plan_gemm_out(int plan, Tensor x_q, Tensor x_scale, Tensor(a!) out, int K) -> ()", &gemm_out);
   m.def("w2a8_plan_gemm_scatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int ld_out, int col_offset, int K) -> ()", &gemm_scatter);
+  m.def("w2a8_plan_gemm_rowscatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int rows_per_dest, int dst_row0, int ld_out, int K) -> ()", &gemm_rowscatter);
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
   m.def("w2a8_plan_query_launch(int plan, int M) -> int[]", &query_launch);

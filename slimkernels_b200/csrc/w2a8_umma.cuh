@@ -90,6 +90,9 @@ struct GemmParams {
   void* out;                  // [M, ld_out] half or bf16
   void* out_extra[7];         // further destinations of the same tile (peer GPUs' buffers), same ld_out
   int n_extra;                // how many of them are used
+  int scatter_rows;           // > 0: row scatter -- token rows [d * scatter_rows, (d + 1) * scatter_rows) go to destination d
+                              // ONLY (0 = out, d = out_extra[d - 1]), at rows scatter_row0 + (m - d * scatter_rows) there
+  int scatter_row0;
   int32_t* partials;          // [groups, M, N] (debug mode) or nullptr
   int* status;                // device status word
   long long ld_out;
@@ -864,17 +867,22 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         named_barrier_sync(1, T::kEpiThreads);
         // destination 0 is this GPU's buffer; the others are peer-mapped buffers of the other ranks (stores over
         // NVLink, so the all-gather of the output overlaps the GEMM tile by tile)
+        // With row scatter the tile has ONE destination, chosen by its token rows, and lands at another row there.
+        int d_first = 0, d_last = p.n_extra, m_dst = m0;
+        if (p.scatter_rows > 0) {
+          d_first = d_last = m0 / p.scatter_rows;
+          m_dst = p.scatter_row0 + (m0 - d_first * p.scatter_rows);
+        }
         if (p.tma_out) {
           // one TMA store per destination moves the whole staged tile (clipped at the edges of the output) while
           // the CTA winds down; the thread only waits until the stores have READ shared memory
           if (threadIdx.x == 0) {
-            tma_store_2d(&tmap_out, n0, m0, smem_base);
-            for (int d = 0; d < p.n_extra; ++d) tma_store_2d(&tmap_extra.map[d], n0, m0, smem_base);
+            for (int d = d_first; d <= d_last; ++d) tma_store_2d(d == 0 ? &tmap_out : &tmap_extra.map[d - 1], n0, m_dst, smem_base);
             bulk_commit_group();
             bulk_wait_group_read0();
           }
         } else
-        for (int d = 0; d <= p.n_extra; ++d) {
+        for (int d = d_first; d <= d_last; ++d) {
           uint16_t* outp = reinterpret_cast<uint16_t*>(d == 0 ? p.out : p.out_extra[d - 1]);
           const bool vec_ok = (n0 + kTileN <= p.N) && (p.ld_out % 8 == 0) &&
                               ((reinterpret_cast<uintptr_t>(outp) & 15) == 0);
@@ -882,16 +890,14 @@ w2a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             // 16 threads x 16 bytes cover one 256-byte row of the tile
             for (int idx = threadIdx.x; idx < BLOCK_M * 16; idx += T::kEpiThreads) {
               const int j = idx >> 4, ch = idx & 15;
-              const int m = m0 + j;
-              if (m < p.M)
-                *reinterpret_cast<uint4*>(outp + static_cast<size_t>(m) * p.ld_out + n0 + ch * 8) =
+              if (m0 + j < p.M)
+                *reinterpret_cast<uint4*>(outp + static_cast<size_t>(m_dst + j) * p.ld_out + n0 + ch * 8) =
                     *reinterpret_cast<const uint4*>(st + j * kTileN + ch * 8);
             }
           } else {
             for (int idx = threadIdx.x; idx < BLOCK_M * kTileN; idx += T::kEpiThreads) {
               const int j = idx >> 7, r = idx & 127;
-              const int m = m0 + j;
-              if (m < p.M && n0 + r < p.N) outp[static_cast<size_t>(m) * p.ld_out + n0 + r] = st[j * kTileN + r];
+              if (m0 + j < p.M && n0 + r < p.N) outp[static_cast<size_t>(m_dst + j) * p.ld_out + n0 + r] = st[j * kTileN + r];
             }
           }
         }

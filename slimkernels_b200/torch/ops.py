@@ -105,6 +105,13 @@ class W2A8Plan:
         pointers: this GPU's buffer first, then peer-mapped buffers of the other ranks)."""
         torch.ops.slimkernels.w2a8_plan_gemm_scatter(self._h, x_q, x_scale, list(out_ptrs), ld_out, col_offset, self.K)
 
+    def gemm_rowscatter(self, x_q, x_scale, out_ptrs, rows_per_dest: int, dst_row0: int, ld_out: int) -> None:
+        """Deals the token rows of the [M, N] result out: rows [d * rows_per_dest, (d + 1) * rows_per_dest) go to
+        the buffer `out_ptrs[d]` only (raw device pointers, rank order; peer-mapped unless this GPU's), at rows
+        dst_row0 .. of it.  The scatter half of a reduce-scatter of K-sharded partial sums."""
+        torch.ops.slimkernels.w2a8_plan_gemm_rowscatter(self._h, x_q, x_scale, list(out_ptrs), rows_per_dest, dst_row0,
+                                                       ld_out, self.K)
+
     def partials(self, x_q):
         return torch.ops.slimkernels.w2a8_plan_partials(self._h, x_q, self.N, self.K, self.group_size)
 

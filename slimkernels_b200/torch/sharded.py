@@ -204,10 +204,18 @@ class KShardedW2A8Gemm:
     [r M/R, (r+1) M/R) of the sum (``forward``), or ``forward_full`` all-gathers them back to [M, N].  The exchange
     moves the partials in the output dtype and sums them in fp32 in rank order (deterministic), rounding once.
     M must be a multiple of the world size.
+
+    ``fused=True``: the scatter half runs inside the GEMM.  Every rank owns a [R, M/R, N] buffer in symmetric memory
+    (two of them, alternating by call); the epilogue of rank r's GEMM stores token-row block d of its partial straight
+    into block r of rank d's buffer (peer stores, one destination per tile, nothing is loaded from a peer), one
+    stream-ordered barrier follows, and every rank adds its R blocks in rank order.  Needs M/R to be a multiple of the
+    GEMM's token tile (256 for M > 128).  The returned rows are a fresh tensor; the receive buffer of a call is
+    overwritten by the second next call.
     """
 
     def __init__(self, w_packed_local, w_scale_local, group=None, group_size=128, zero_point=1,
-                 out_dtype=torch.float16, plan_factory=W2A8Plan, exchange_timeout_s=None, control_group=None):
+                 out_dtype=torch.float16, plan_factory=W2A8Plan, exchange_timeout_s=None, control_group=None,
+                 fused=False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -218,8 +226,41 @@ class KShardedW2A8Gemm:
         self.timeout_s = exchange_timeout_s
         self._live = _Liveness(control_group, exchange_timeout_s, self.rank)
         self._step = 0
+        self.fused = fused and self.world > 1
+        self._symm = {}
+
+    def _symmetric(self, M, device):
+        """Two [R, M/R, N] receive buffers in symmetric memory, each with every rank's pointer to it in rank order."""
+        key = (M, device)
+        if key not in self._symm:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
+            import torch.distributed._symmetric_memory as symm_mem
+            group = self.group if self.group is not None else dist.group.WORLD
+            slots = []
+            for _ in range(2):
+                buf = symm_mem.empty((M, self.N), dtype=self.out_dtype, device=device)
+                hdl = symm_mem.rendezvous(buf, group)
+                ptrs = [int(hdl.buffer_ptrs[d]) for d in range(self.world)]
+                slots.append((buf, hdl, ptrs))
+            self._symm[key] = slots
+        return self._symm[key]
+
+    def forward_fused(self, x_q_local, x_scale_local):
+        M = x_q_local.shape[0]
+        if M % self.world != 0:
+            raise ValueError(f"M={M} must be a multiple of the world size {self.world}")
+        rows = M // self.world
+        self._live.check(self._step)
+        buf, hdl, ptrs = self._symmetric(M, x_q_local.device)[self._step & 1]
+        # block d of this rank's partial -> block `rank` of rank d's buffer
+        self.plan.gemm_rowscatter(x_q_local, x_scale_local, ptrs, rows, self.rank * rows, self.N)
+        hdl.barrier()          # every rank's blocks have landed
+        self._step += 1
+        return buf.view(self.world, rows, self.N).float().sum(dim=0).to(self.out_dtype)
 
     def forward(self, x_q_local, x_scale_local):
+        if self.fused:
+            return self.forward_fused(x_q_local, x_scale_local)
         M = x_q_local.shape[0]
         partial = self.plan.gemm(x_q_local, x_scale_local)                   # [M, N], this rank's share of the sum
         if self.world == 1:

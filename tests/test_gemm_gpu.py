@@ -3,6 +3,8 @@
 Bars: per-group int32 partial sums bit-exact; outputs within 1e-2 max-abs of the fp32 dequantise-then-matmul
 reference path (plus half an output ulp is already inside that bound for these value ranges).
 """
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -237,6 +239,34 @@ def test_pair_kernel_needs_an_even_number_of_feature_tiles():
     assert dp.plan.query_launch(300)["kernel"] == capi.KERNEL_TCGEN05
     assert dp.force(kernel=capi.KERNEL_TCGEN05_PAIR).plan.query_launch(300)["kernel"] == capi.KERNEL_TCGEN05
     assert np.abs(to_np(dp.gemm()) - O.w2a8_gemm_dequant_path(x_q, xs, wp, ws)).max() <= TOL
+
+
+@pytest.mark.parametrize("ld_extra", [0, 8, 3])      # TMA stores, TMA stores into a wider buffer, thread stores (odd pitch)
+def test_row_scatter_deals_token_rows_to_their_destinations(ld_extra):
+    """sk_w2a8_gemm_rowscatter on one GPU with two local destination buffers standing in for two ranks' buffers."""
+    M, N, K, rows = 512, 384, 512, 256
+    x_q, xs, wp, ws = random_problem(M, N, K, 128, seed=77)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    y = dp.gemm()
+    ld = N + ld_extra
+    bufs = [torch.zeros(2 * rows, ld, dtype=torch.float16, device="cuda") for _ in range(2)]
+    lib = capi.load()
+    ptrs = (ctypes.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    rc = lib.sk_w2a8_gemm_rowscatter(dp.plan.handle, M, dp.x_q.data_ptr(), K, dp.x_scale.data_ptr(), ptrs, 2, rows, rows,
+                                     ld, dp.stream())     # "this rank" is rank 1: its blocks land at rows 256..511
+    assert rc == capi.SK_OK
+    torch.cuda.synchronize()
+    assert dp.plan.device_status() == 0
+    for d in range(2):
+        assert torch.equal(bufs[d][rows:, :N], y[d * rows:(d + 1) * rows])
+        assert not bufs[d][:rows].any() and not bufs[d][:, N:].any()
+    # rows per destination that are not whole token tiles, a decode-sized call, a wrong total: refused, nothing launched
+    assert lib.sk_w2a8_gemm_rowscatter(dp.plan.handle, M, dp.x_q.data_ptr(), K, dp.x_scale.data_ptr(), ptrs, 2, rows - 1, 0,
+                                       ld, dp.stream()) == capi.SK_ERR_BAD_SHAPE
+    assert lib.sk_w2a8_gemm_rowscatter(dp.plan.handle, 32, dp.x_q.data_ptr(), K, dp.x_scale.data_ptr(), ptrs, 2, 16, 0,
+                                       ld, dp.stream()) == capi.SK_ERR_UNAVAILABLE
+    assert lib.sk_w2a8_gemm_rowscatter(dp.plan.handle, 128, dp.x_q.data_ptr(), K, dp.x_scale.data_ptr(), ptrs, 2, 64, 0,
+                                       ld, dp.stream()) == capi.SK_ERR_UNAVAILABLE      # 128-token tile, 64 rows each
 
 
 def test_checker_kernel_matches_oracle():

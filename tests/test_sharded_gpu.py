@@ -123,7 +123,7 @@ def test_two_gpu_fused_result_can_be_read_while_the_next_step_runs(built_libs):
         assert err <= 1e-2
 
 
-def _worker_k(rank, world, port, q):
+def _worker_k(rank, world, port, q, fused=False):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -134,17 +134,22 @@ def _worker_k(rank, world, port, q):
         from oracle import w2a8_oracle as O
         from slimkernels_b200 import workloads as W
         from slimkernels_b200.torch.sharded import KShardedW2A8Gemm, shard_weight_k
-        M, N, K, G = 256, 512, 2048, 128
+        M, N, K, G = (1024, 384, 2048, 128) if fused else (256, 512, 2048, 128)   # fused: M/R = 2 tiles of 256 tokens
         x_q, _, w_packed, w_scale = W.make_problem(M, N, K, G, seed=2)
         scales = np.random.default_rng(9).uniform(0.005, 0.02, size=(world, M)).astype(np.float32)
         per = K // world
         wl, sl = shard_weight_k(torch.from_numpy(w_packed).to(dev), torch.from_numpy(w_scale).to(dev), world, rank, G)
-        op = KShardedW2A8Gemm(wl, sl, group_size=G)
+        op = KShardedW2A8Gemm(wl, sl, group_size=G, fused=fused)
         xl = torch.from_numpy(np.ascontiguousarray(x_q[:, rank * per:(rank + 1) * per])).to(dev)
         xs = torch.from_numpy(scales[rank]).to(dev)
         mine = op(xl, xs)
         full = op.forward_full(xl, xs)
         torch.cuda.synchronize(dev)
+        if fused:
+            # the fused exchange and the NCCL one add the same fp16 partials in the same order: bit-identical
+            plain = KShardedW2A8Gemm(wl, sl, group_size=G)(xl, xs)
+            assert torch.equal(mine, plain)
+            assert torch.equal(op(xl, xs), mine) and torch.equal(op(xl, xs), mine)    # both receive buffers
         ref = sum(O.w2a8_gemm_dequant_path(np.ascontiguousarray(x_q[:, r * per:(r + 1) * per]), scales[r],
                                            np.ascontiguousarray(w_packed[:, r * per // 4:(r + 1) * per // 4]),
                                            w_scale[r * per // G:(r + 1) * per // G], G) for r in range(world))
@@ -156,14 +161,16 @@ def _worker_k(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_k_sharded_reduce_scatter(built_libs):
-    """K-sharded down-projection style GEMM: partial products on each GPU, reduce-scatter by token rows."""
+@pytest.mark.parametrize("fused", [False, True])
+def test_two_gpu_k_sharded_reduce_scatter(built_libs, fused):
+    """K-sharded down-projection style GEMM: partial products on each GPU, reduce-scatter by token rows -- through
+    NCCL after the GEMM, or (fused) by peer stores from the GEMM's epilogue into the owning rank's receive buffer."""
     import torch.multiprocessing as mp
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker_k, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker_k, args=(r, world, port, q, fused)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
