@@ -556,6 +556,54 @@ def measure_k_sharded(wl, seed, args, dev, world, rank, steps):
     return out
 
 
+def measure_tp_mlp(seed, dev, world, rank, steps):
+    """Llama-3-70B MLP block (hidden 8192, intermediate 28672, 4096 tokens) tensor-parallel over the ranks: gate+up
+    split by output features, SiLU*up local, down split along K with the reduce-scatter fused into its epilogue (or
+    NCCL all-to-all after it).  One exchange per block.  Device-timed, max over ranks; the two exchange variants must
+    agree bit for bit (parity against the oracle is the 2-GPU unit test's job at a size the oracle can do)."""
+    import torch
+    import torch.distributed as dist
+    from slimkernels_b200.torch.sharded import TensorParallelW2A8LlamaMLP
+    M, H, I, G = 4096, 8192, 28672, 128
+    per = I // world
+    if I % (world * G) or M % world or (M // world) % 256:
+        return {"skipped": f"intermediate {I} / tokens {M} do not split over {world} ranks in whole groups and tiles"}
+    rng = np.random.default_rng([seed, 99, rank])
+    t = lambda a: torch.from_numpy(a).to(dev)
+    gl = t(rng.integers(0, 256, size=(2 * per, H // 4), dtype=np.uint8))
+    gs = t(rng.uniform(0.001, 0.01, size=(H // G, 2 * per)).astype(np.float16))
+    dl = t(rng.integers(0, 256, size=(H, per // 4), dtype=np.uint8))
+    ds = t(rng.uniform(0.001, 0.01, size=(per // G, H)).astype(np.float16))
+    x = t((np.random.default_rng([seed, 98]).standard_normal((M, H)) * 0.5).astype(np.float16))   # replicated
+    stream = torch.cuda.current_stream(dev)
+    ops = 2.0 * M * (2 * I * H + H * I)
+    out = {"workload": "llama3_70b_mlp_block_tensor_parallel", "M": M, "hidden": H, "intermediate": I,
+           "bytes_sent_per_rank": (world - 1) * (M // world) * H * 2,
+           "launches_per_block": "quantise, gate+up GEMM, SiLU*up + re-quantise, down GEMM (+ reduce-scatter), fp32 sum of the partials"}
+    res = {}
+    for fused in (True, False):
+        block = TensorParallelW2A8LlamaMLP(gl, gs, dl, ds, group_size=G, fused=fused)
+        for _ in range(3):
+            block(x)
+        dist.barrier(); torch.cuda.synchronize(dev)
+        ms = time_events(lambda: block(x), steps, stream)
+        dist.barrier(); torch.cuda.synchronize(dev)
+        tt = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+        res[fused] = block(x).clone()
+        out["fused_peer_stores" if fused else "nccl_all_to_all"] = {"ms_per_block": round(ms, 4),
+                                                                    "tops": round(ops / (ms * 1e-3) / 1e12, 2)}
+        del block
+    same = torch.tensor([1 if torch.equal(res[True], res[False]) else 0], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    out["fused_equals_nccl_bitwise"] = bool(same.item())
+    out["finite"] = bool(torch.isfinite(res[True].float()).all().item())
+    del gl, gs, dl, ds, x, res
+    torch.cuda.empty_cache()
+    return out
+
+
 def measure_workload(wl, seed, args, dev, world, rank, fused, steps, peaks, with_e2e=False, with_parity=True):
     """One N-sharded GEMM (+ exchange) workload: device-timed step (max over ranks), this rank's GEMM alone (warmed,
     min / median / max over ranks), exchange figures, parity.  Returns a dict (same on every rank)."""
@@ -759,6 +807,9 @@ def run_ours(args):
             ks = measure_k_sharded(WORKLOAD_DOWN, 2, args, dev, world, rank, few)
             k_sharded_ok = ks.pop("_ok", True)
             extra["down_proj_k_sharded"] = ks
+            tp = measure_tp_mlp(3, dev, world, rank, few)
+            k_sharded_ok = k_sharded_ok and tp.get("fused_equals_nccl_bitwise", True) and tp.get("finite", True)
+            extra["mlp_block_tensor_parallel"] = tp
         line["config3"] = extra
 
     if world == 1 and not args.no_sweeps:

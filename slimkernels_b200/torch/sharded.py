@@ -285,3 +285,51 @@ class KShardedW2A8Gemm:
         return full
 
     __call__ = forward
+
+
+def shard_gate_up(gate_up_packed, gate_up_scale, world: int, rank: int):
+    """This rank's share of a fused gate+up weight ([2*inter, K/4] packed, gate rows first; scales [K/G, 2*inter]):
+    gate rows [r I/R, (r+1) I/R) followed by the up rows of the same features, so that SiLU(gate)*up stays local."""
+    two_i = gate_up_packed.shape[0]
+    if two_i % (2 * world) != 0:
+        raise ValueError(f"2*inter={two_i} must be a multiple of 2*world_size={2 * world}")
+    inter = two_i // 2
+    per = inter // world
+    rows = torch.cat([torch.arange(rank * per, (rank + 1) * per), torch.arange(inter + rank * per, inter + (rank + 1) * per)])
+    rows = rows.to(gate_up_packed.device)
+    return gate_up_packed[rows].contiguous(), gate_up_scale[:, rows].contiguous()
+
+
+class TensorParallelW2A8LlamaMLP:
+    """down( SiLU(gate(x)) * up(x) ) over R ranks with ONE exchange: gate+up split along their output features
+    (``shard_gate_up``), SiLU*up and its re-quantisation local to the rank (per-token scales over the rank's slice of
+    the intermediate features), down split along K (``shard_weight_k``) with the partial sums reduce-scattered by
+    token rows -- inside the down GEMM's epilogue when ``fused`` (``KShardedW2A8Gemm``).
+
+    x fp16 [M, hidden], replicated.  ``forward`` returns rows [r M/R, (r+1) M/R) of the block's output,
+    ``forward_full`` all-gathers [M, hidden].  Numerically this is the sum over ranks of the single-GPU block applied to
+    each rank's slices (each partial rounded to the output dtype once before the fp32 sum).
+    """
+
+    def __init__(self, gate_up_packed_local, gate_up_scale_local, down_packed_local, down_scale_local, group=None,
+                 group_size=128, zero_point=1, out_dtype=torch.float16, fused=True, exchange_timeout_s=None,
+                 control_group=None, plan_factory=W2A8Plan):
+        self.gate_up = plan_factory(gate_up_packed_local, gate_up_scale_local, group_size=group_size,
+                                    zero_point=zero_point, out_dtype=torch.float16)
+        self.down = KShardedW2A8Gemm(down_packed_local, down_scale_local, group=group, group_size=group_size,
+                                     zero_point=zero_point, out_dtype=out_dtype, plan_factory=plan_factory,
+                                     exchange_timeout_s=exchange_timeout_s, control_group=control_group, fused=fused)
+
+    def _hidden(self, x):
+        from .modules import quantize_activation_int8, silu_mul_quantize_int8
+        x_q, x_s = quantize_activation_int8(x)
+        gate_up = self.gate_up.gemm(x_q, x_s)                 # [M, 2 I/R]: this rank's gate columns, then its up columns
+        return silu_mul_quantize_int8(gate_up)                # int8 [M, I/R], fp32 [M]
+
+    def forward(self, x):
+        return self.down(*self._hidden(x))
+
+    def forward_full(self, x):
+        return self.down.forward_full(*self._hidden(x))
+
+    __call__ = forward

@@ -205,3 +205,21 @@ def test_missing_rank_is_noticed_by_the_liveness_barrier_before_the_launch():
     assert res[0][1] == "timeout", res[0]
     assert "liveness" in res[0][2][0]
     assert res[0][3] < 5.5
+
+
+def test_shard_gate_up_keeps_gate_and_up_rows_of_the_same_features_together():
+    from slimkernels_b200.torch.sharded import shard_gate_up
+    inter, world = 8, 4
+    packed = torch.arange(2 * inter * 3, dtype=torch.uint8).view(2 * inter, 3)
+    scale = torch.arange(2 * 2 * inter, dtype=torch.float16).view(2, 2 * inter)
+    gates, ups = [], []
+    for r in range(world):
+        p_l, s_l = shard_gate_up(packed, scale, world, r)
+        per = inter // world
+        assert p_l.shape == (2 * per, 3) and s_l.shape == (2, 2 * per)
+        gates.append(p_l[:per]); ups.append(p_l[per:])
+        assert torch.equal(s_l[:, :per], scale[:, r * per:(r + 1) * per])
+        assert torch.equal(s_l[:, per:], scale[:, inter + r * per:inter + (r + 1) * per])
+    assert torch.equal(torch.cat(gates), packed[:inter]) and torch.equal(torch.cat(ups), packed[inter:])
+    with pytest.raises(ValueError):
+        shard_gate_up(packed, scale, 3, 0)

@@ -179,3 +179,66 @@ def test_two_gpu_k_sharded_reduce_scatter(built_libs, fused):
         assert p.exitcode == 0
     for _, err_mine, err_full in results:
         assert err_mine <= 1e-2 and err_full <= 1e-2
+
+
+def _worker_tp(rank, world, port, q):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from oracle import w2a8_oracle as O
+        from slimkernels_b200.torch.sharded import TensorParallelW2A8LlamaMLP, shard_gate_up, shard_weight_k
+        M, H, I, G = 512, 512, 1024, 128          # M/R = one 256-token tile, I/R = 512 = 4 groups of the down projection
+        rng = np.random.default_rng(5)
+        x = (rng.standard_normal((M, H)) * 0.5).astype(np.float16)
+        gu_p = rng.integers(0, 256, size=(2 * I, H // 4), dtype=np.uint8)
+        gu_s = rng.uniform(0.001, 0.01, size=(H // G, 2 * I)).astype(np.float16)
+        dn_p = rng.integers(0, 256, size=(H, I // 4), dtype=np.uint8)
+        dn_s = rng.uniform(0.001, 0.01, size=(I // G, H)).astype(np.float16)
+        t = lambda a: torch.from_numpy(a).to(dev)
+        gl, gs = shard_gate_up(t(gu_p), t(gu_s), world, rank)
+        dl, ds = shard_weight_k(t(dn_p), t(dn_s), world, rank, G)
+        outs = {}
+        for fused in (True, False):
+            block = TensorParallelW2A8LlamaMLP(gl, gs, dl, ds, group_size=G, fused=fused)
+            outs[fused] = (block(t(x)).clone(), block.forward_full(t(x)).clone())
+        torch.cuda.synchronize(dev)
+        assert torch.equal(outs[True][0], outs[False][0]) and torch.equal(outs[True][1], outs[False][1])
+        # reference: the single-GPU block of the oracle on every rank's slices, partials rounded to fp16, summed
+        per = I // world
+        ref = np.zeros((M, H), dtype=np.float32)
+        for r in range(world):
+            rows = np.concatenate([np.arange(r * per, (r + 1) * per), np.arange(I + r * per, I + (r + 1) * per)])
+            part = O.llama_mlp(x, np.ascontiguousarray(gu_p[rows]), np.ascontiguousarray(gu_s[:, rows]),
+                               np.ascontiguousarray(dn_p[:, r * per // 4:(r + 1) * per // 4]),
+                               dn_s[r * per // G:(r + 1) * per // G], G)
+            ref += part.astype(np.float16).astype(np.float32)
+        mr = M // world
+        mine, full = outs[True]
+        q.put((rank, float(np.abs(mine.float().cpu().numpy() - ref[rank * mr:(rank + 1) * mr]).max()),
+               float(np.abs(full.float().cpu().numpy() - ref).max()), float(np.abs(ref).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_tensor_parallel_mlp_block(built_libs):
+    """Llama MLP block over two GPUs with one exchange: gate+up split by features, SiLU*up local, down split along K
+    with the reduce-scatter in its epilogue.  Checked against the oracle's block applied to each rank's slices."""
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_tp, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for _, err_mine, err_full, scale in results:
+        assert err_mine <= 1e-2 * max(1.0, scale) and err_full <= 1e-2 * max(1.0, scale)
