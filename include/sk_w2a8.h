@@ -142,6 +142,13 @@ int sk_w2a8_gemm_rowscatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, in
                             void* const* outs, int n_outs, int64_t rows_per_dest, int64_t dst_row0, int64_t ld_out,
                             sk_stream_t stream);
 
+/* The add half of a reduce-scatter of K-sharded partial sums: out[r, n] = round( sum_b fp32(blocks[b][r][n]) ), the
+ * n_blocks (1..64) row blocks [rows, N] of 16-bit floats (out_dtype says which) added in fp32 in block order and
+ * rounded once.  Block b starts block_stride elements after block b - 1; row pitches ld / ld_out; N % 8 == 0,
+ * 16-byte aligned pointers and pitches.  One pass over the data.  No counterpart in the reference. */
+int sk_sum_row_blocks(const void* blocks, int n_blocks, int64_t block_stride, int64_t ld, int64_t rows, int64_t N,
+                      void* out, int64_t ld_out, int out_dtype, sk_stream_t stream);
+
 /* Same contraction, but stores the exact per-group integer partial sums
  * partials[g, m, n] (int32, [K/G, M, N] contiguous) instead of the scaled output. */
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,

@@ -6,6 +6,7 @@
 // Both kernels are HBM-bound row passes with 16-byte loads; the row is kept in registers between the max pass and the
 // quantise pass (one CTA per row for the plain quantiser, a cluster of CTAs per row for the SiLU one).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -240,6 +241,54 @@ silu_mul_quantize_twopass_kernel(const __half* __restrict__ gate_up, long long l
     for (int j = 0; j < 8; ++j)
       w[j >> 2] |= (static_cast<uint32_t>(quantize_one(h[j], s)) & 0xffu) << (8 * (j & 3));
     qrow[v] = make_uint2(w[0], w[1]);
+  }
+}
+
+
+// Sum of n_blocks row blocks [rows][N] (16-bit floats, block pitch `block_stride` elements, row pitch ld) in fp32 in
+// block order, rounded once to the same 16-bit type: the add half of the reduce-scatter of K-sharded partial sums.
+// 8 elements (16 bytes) per thread; N % 8 == 0.
+template <bool BF16>
+__global__ void sum_row_blocks_kernel(const uint16_t* __restrict__ blocks, long long block_stride, long long ld,
+                                      int n_blocks, long long rows, int N, uint16_t* __restrict__ out, long long ld_out) {
+  const int vec_per_row = N / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int b = 0; b < n_blocks; ++b) {
+      const uint4 v = *reinterpret_cast<const uint4*>(blocks + b * block_stride + r * ld + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        if constexpr (BF16) {
+          lo = __uint_as_float(w[j] << 16);
+          hi = __uint_as_float(w[j] & 0xffff0000u);
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+          lo = f.x; hi = f.y;
+        }
+        acc[2 * j] += lo;
+        acc[2 * j + 1] += hi;
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if constexpr (BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o[j] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        o[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + r * ld_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 

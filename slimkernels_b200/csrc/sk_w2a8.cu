@@ -1330,6 +1330,30 @@ int sk_w2a8_mlp_forward_static(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_
   return rc;
 }
 
+int sk_sum_row_blocks(const void* blocks, int n_blocks, int64_t block_stride, int64_t ld, int64_t rows, int64_t N,
+                      void* out, int64_t ld_out, int out_dtype, sk_stream_t stream) {
+  if (!blocks || !out) return SK_ERR_NULL_POINTER;
+  if (n_blocks < 1 || n_blocks > 64) return SK_ERR_BAD_ARGUMENT;
+  if (out_dtype != SK_OUT_F16 && out_dtype != SK_OUT_BF16) return SK_ERR_BAD_ARGUMENT;
+  if (rows <= 0 || N <= 0 || (N % 8) != 0 || ld < N || ld_out < N || N > 0x7fffffffLL) return SK_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(blocks) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (ld % 8) || (ld_out % 8) ||
+      (block_stride % 8))
+    return SK_ERR_BAD_ALIGNMENT;
+  const long long total = rows * (N / 8);
+  const int threads = 256;
+  const long long want = (total + threads - 1) / threads;
+  const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+  const auto st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == SK_OUT_BF16)
+    sk::sum_row_blocks_kernel<true><<<grid, threads, 0, st>>>(static_cast<const uint16_t*>(blocks), block_stride, ld, n_blocks,
+                                                             rows, static_cast<int>(N), static_cast<uint16_t*>(out), ld_out);
+  else
+    sk::sum_row_blocks_kernel<false><<<grid, threads, 0, st>>>(static_cast<const uint16_t*>(blocks), block_stride, ld, n_blocks,
+                                                              rows, static_cast<int>(N), static_cast<uint16_t*>(out), ld_out);
+  if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
+  return SK_OK;
+}
+
 #ifdef SK_TRACE
 // Diagnostic build only: device buffer of 5 x 64 clock stamps written by CTA (0,0,0) of the next launches.
 int sk_w2a8_set_trace_buffer(long long* device_buffer) {

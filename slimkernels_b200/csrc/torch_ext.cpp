@@ -115,6 +115,21 @@ void gemm_rowscatter(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_
         "w2a8_gemm_rowscatter");
 }
 
+// blocks [B, rows, N] (half or bfloat16, contiguous) -> [rows, N]: fp32 sum over B in index order, rounded once
+at::Tensor sum_row_blocks(const at::Tensor& blocks) {
+  TORCH_CHECK(blocks.is_cuda() && blocks.dim() == 3 && blocks.is_contiguous(), "blocks must be a contiguous CUDA tensor [B, rows, N]");
+  TORCH_CHECK(blocks.scalar_type() == at::kHalf || blocks.scalar_type() == at::kBFloat16, "blocks must be float16 or bfloat16");
+  const int64_t B = blocks.size(0), rows = blocks.size(1), N = blocks.size(2);
+  at::Tensor out = at::empty({rows, N}, blocks.options());
+  if (rows == 0 || N == 0) return out;
+  c10::cuda::CUDAGuard guard(blocks.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check(sk_sum_row_blocks(blocks.data_ptr(), static_cast<int>(B), rows * N, N, rows, N, out.data_ptr(), N,
+                          blocks.scalar_type() == at::kBFloat16 ? SK_OUT_BF16 : SK_OUT_F16, stream.stream()),
+        "sum_row_blocks");
+  return out;
+}
+
 at::Tensor gemm(int64_t handle, const at::Tensor& x_q, const at::Tensor& x_scale, int64_t N, int64_t K, bool bf16_out) {
   at::Tensor out = at::empty({x_q.size(0), N}, x_q.options().dtype(bf16_out ? at::kBFloat16 : at::kHalf));
   gemm_out(handle, x_q, x_scale, out, K);
@@ -326,6 +341,7 @@ TORCH_LIBRARY(slimkernels, m) {
   m.def("w2a8_plan_gemm_out(int plan, Tensor x_q, Tensor x_scale, Tensor(a!) out, int K) -> ()", &gemm_out);
   m.def("w2a8_plan_gemm_scatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int ld_out, int col_offset, int K) -> ()", &gemm_scatter);
   m.def("w2a8_plan_gemm_rowscatter(int plan, Tensor x_q, Tensor x_scale, int[] out_ptrs, int rows_per_dest, int dst_row0, int ld_out, int K) -> ()", &gemm_rowscatter);
+  m.def("sum_row_blocks(Tensor blocks) -> Tensor", &sum_row_blocks);
   m.def("w2a8_plan_partials(int plan, Tensor x_q, int N, int K, int group_size) -> Tensor", &partials);
   m.def("w2a8_plan_device_status(int plan) -> int", &device_status);
   m.def("w2a8_plan_query_launch(int plan, int M) -> int[]", &query_launch);

@@ -229,6 +229,15 @@ class KShardedW2A8Gemm:
         self.fused = fused and self.world > 1
         self._symm = {}
 
+    def _add_blocks(self, blocks):
+        """[R, rows, N] partial sums -> [rows, N]: fp32 sum in rank order, rounded once."""
+        if blocks.is_cuda and self.N % 8 == 0:
+            return torch.ops.slimkernels.sum_row_blocks(blocks)          # one pass over the data
+        acc = blocks[0].float()
+        for r in range(1, blocks.shape[0]):
+            acc = acc + blocks[r].float()
+        return acc.to(self.out_dtype)
+
     def _symmetric(self, M, device):
         """Two [R, M/R, N] receive buffers in symmetric memory, each with every rank's pointer to it in rank order."""
         key = (M, device)
@@ -256,7 +265,7 @@ class KShardedW2A8Gemm:
         self.plan.gemm_rowscatter(x_q_local, x_scale_local, ptrs, rows, self.rank * rows, self.N)
         hdl.barrier()          # every rank's blocks have landed
         self._step += 1
-        return buf.view(self.world, rows, self.N).float().sum(dim=0).to(self.out_dtype)
+        return self._add_blocks(buf.view(self.world, rows, self.N))
 
     def forward(self, x_q_local, x_scale_local):
         if self.fused:
@@ -273,7 +282,7 @@ class KShardedW2A8Gemm:
         work = dist.all_to_all_single(recv, partial.contiguous(), group=self.group, async_op=True)
         _wait_with_limit(work, self.rank, self._step, "exchange of the partial sums", self.timeout_s)
         self._step += 1
-        return recv.view(self.world, rows, self.N).float().sum(dim=0).to(self.out_dtype)
+        return self._add_blocks(recv.view(self.world, rows, self.N))
 
     def forward_full(self, x_q_local, x_scale_local):
         mine = self.forward(x_q_local, x_scale_local)

@@ -116,3 +116,23 @@ def test_mlp_forward_runs_on_the_plans_device_whatever_is_current():
     torch.cuda.synchronize(dev)
     y_ref = O.llama_mlp(x, gu_p, gu_s, dn_p, dn_s, 128)
     assert np.abs(out.float().cpu().numpy() - y_ref).max() <= 1e-2 * np.abs(y_ref).max() + 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_sum_row_blocks_adds_in_block_order_in_fp32(dtype):
+    """The add half of the reduce-scatter: fp32 sum of the row blocks in index order, rounded once (bit-exact against
+    the same sum spelled out in torch)."""
+    from slimkernels_b200.torch import load_extension
+    load_extension()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    blocks = (torch.randn(5, 300, 264, device="cuda", generator=g) * 3).to(dtype)
+    acc = blocks[0].float()
+    for b in range(1, 5):
+        acc = acc + blocks[b].float()
+    out = torch.ops.slimkernels.sum_row_blocks(blocks)
+    assert out.dtype == dtype and torch.equal(out, acc.to(dtype))
+    assert torch.equal(torch.ops.slimkernels.sum_row_blocks(blocks[:1]), blocks[0])
+    with pytest.raises(RuntimeError):
+        torch.ops.slimkernels.sum_row_blocks(blocks[:, :, :260])          # not contiguous
+    with pytest.raises(RuntimeError):
+        torch.ops.slimkernels.sum_row_blocks(blocks[:, :, :4].contiguous())   # N % 8 != 0
