@@ -322,7 +322,9 @@ class TensorParallelW2A8LlamaMLP:
 
     def __init__(self, gate_up_packed_local, gate_up_scale_local, down_packed_local, down_scale_local, group=None,
                  group_size=128, zero_point=1, out_dtype=torch.float16, fused=True, exchange_timeout_s=None,
-                 control_group=None, plan_factory=W2A8Plan):
+                 control_group=None, plan_factory=W2A8Plan, activation_ops=None):
+        # activation_ops: (quantize_activation_int8, silu_mul_quantize_int8) stand-ins, for tests without a GPU
+        self._act = activation_ops
         self.gate_up = plan_factory(gate_up_packed_local, gate_up_scale_local, group_size=group_size,
                                     zero_point=zero_point, out_dtype=torch.float16)
         self.down = KShardedW2A8Gemm(down_packed_local, down_scale_local, group=group, group_size=group_size,
@@ -330,7 +332,10 @@ class TensorParallelW2A8LlamaMLP:
                                      exchange_timeout_s=exchange_timeout_s, control_group=control_group, fused=fused)
 
     def _hidden(self, x):
-        from .modules import quantize_activation_int8, silu_mul_quantize_int8
+        if self._act is not None:
+            quantize_activation_int8, silu_mul_quantize_int8 = self._act
+        else:
+            from .modules import quantize_activation_int8, silu_mul_quantize_int8
         x_q, x_s = quantize_activation_int8(x)
         gate_up = self.gate_up.gemm(x_q, x_s)                 # [M, 2 I/R]: this rank's gate columns, then its up columns
         return silu_mul_quantize_int8(gate_up)                # int8 [M, I/R], fp32 [M]

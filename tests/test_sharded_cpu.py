@@ -223,3 +223,68 @@ def test_shard_gate_up_keeps_gate_and_up_rows_of_the_same_features_together():
     assert torch.equal(torch.cat(gates), packed[:inter]) and torch.equal(torch.cat(ups), packed[inter:])
     with pytest.raises(ValueError):
         shard_gate_up(packed, scale, 3, 0)
+
+
+def _worker_tp(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import w2a8_oracle as O
+        from slimkernels_b200.torch.sharded import TensorParallelW2A8LlamaMLP, shard_gate_up, shard_weight_k
+        M, H, I, G = 4, 256, 512, 128
+        rng = np.random.default_rng(5)
+        x = (rng.standard_normal((M, H)) * 0.5).astype(np.float16)
+        gu_p = rng.integers(0, 256, size=(2 * I, H // 4), dtype=np.uint8)
+        gu_s = rng.uniform(0.001, 0.01, size=(H // G, 2 * I)).astype(np.float16)
+        dn_p = rng.integers(0, 256, size=(H, I // 4), dtype=np.uint8)
+        dn_s = rng.uniform(0.001, 0.01, size=(I // G, H)).astype(np.float16)
+
+        def quantize(t):                      # CPU stand-ins for the two activation kernels: the oracle's rules
+            qv, sv = O.quantize_activation_int8(t.numpy())
+            return torch.from_numpy(qv), torch.from_numpy(sv)
+
+        def silu_mul_quantize(gate_up):
+            gu = gate_up.numpy().astype(np.float32)
+            inter = gu.shape[1] // 2
+            g, u = gu[:, :inter], gu[:, inter:]
+            return quantize(torch.from_numpy(((g / (1.0 + np.exp(-g))) * u).astype(np.float32)))
+
+        gl, gs = shard_gate_up(torch.from_numpy(gu_p), torch.from_numpy(gu_s), world, rank)
+        dl, ds = shard_weight_k(torch.from_numpy(dn_p), torch.from_numpy(dn_s), world, rank, G)
+        block = TensorParallelW2A8LlamaMLP(gl, gs, dl, ds, group_size=G, fused=False, plan_factory=OraclePlan,
+                                           activation_ops=(quantize, silu_mul_quantize))
+        mine = block(torch.from_numpy(x))
+        full = block.forward_full(torch.from_numpy(x))
+        per = I // world
+        ref = np.zeros((M, H), dtype=np.float32)
+        for r in range(world):
+            rows = np.concatenate([np.arange(r * per, (r + 1) * per), np.arange(I + r * per, I + (r + 1) * per)])
+            part = O.llama_mlp(x, np.ascontiguousarray(gu_p[rows]), np.ascontiguousarray(gu_s[:, rows]),
+                               np.ascontiguousarray(dn_p[:, r * per // 4:(r + 1) * per // 4]),
+                               dn_s[r * per // G:(r + 1) * per // G], G)
+            ref += part.astype(np.float16).astype(np.float32)
+        mr = M // world
+        q.put((rank, float(np.abs(mine.float().numpy() - ref[rank * mr:(rank + 1) * mr]).max()),
+               float(np.abs(full.float().numpy() - ref).max()), tuple(mine.shape), tuple(full.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_tensor_parallel_mlp_block_on_cpu():
+    """The block's host logic (which rows of gate+up a rank owns, local SiLU*up with per-rank token scales, K-sharded
+    down, reduce-scatter by token rows) on two gloo ranks, with the oracle standing in for every device kernel."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_tp, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, err_mine, err_full, shape_mine, shape_full in results:
+        assert shape_mine == (2, 256) and shape_full == (4, 256)
+        assert err_mine <= 1e-2 and err_full <= 1e-2
