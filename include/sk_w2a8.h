@@ -101,7 +101,9 @@ int sk_w2a8_unrepack(const uint8_t* w_tiled, int64_t N, int64_t K, uint8_t* w_pa
  * borrows one), allocates a 4-byte device status word.  Stands where gemm_tn builds its tilers, smem
  * layouts and tensor maps on every call (wgmma_sm90_W2A8.cu:448-466).  Synchronises `device` once.
  * With group size 128 the plan also makes a private copy of the scales in the order its decode kernels
- * stream them, and a scratch buffer for partial sums of its balanced-split decode kernel (a few MiB):
+ * stream them, and -- for weight matrices large enough that the balanced-split decode kernel is their default, or
+ * on the first SK_OPT_KERNEL = 5 / SK_OPT_STREAM_CTAS request -- a scratch buffer for that kernel's partial sums
+ * (3-20 MiB):
  * w_scale_f16 must still outlive the plan (the other kernels read it), and a change of its contents
  * after plan creation is not picked up consistently -- make a new plan instead. */
 int sk_w2a8_plan_create(sk_w2a8_plan** plan, int device, int64_t N, int64_t K, int group_size,

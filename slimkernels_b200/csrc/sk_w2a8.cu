@@ -886,7 +886,10 @@ int sk_w2a8_plan_create(sk_w2a8_plan** out, int device, int64_t N, int64_t K, in
       if (e != cudaSuccess) rc = sk::cuda_fail(plan, e);
     }
   }
-  if (rc == SK_OK) rc = sk::stream_setup(plan, 0);
+  // The balanced-split decode kernel's scratch is allocated here only where that kernel is the default (large weight
+  // matrices, see choose()); elsewhere on request (SK_OPT_KERNEL = 5 / SK_OPT_STREAM_CTAS, set-up calls).
+  if (rc == SK_OK && static_cast<long long>(plan->n_tiles) * plan->k_blocks >= 64LL * plan->sm_count)
+    rc = sk::stream_setup(plan, 0);
   if (cur >= 0 && cur != device) (void)cudaSetDevice(cur);
   if (rc != SK_OK) {
     if (plan->status) cudaFree(plan->status);
@@ -934,7 +937,15 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
     case SK_OPT_KERNEL:
       if (value < 0 || value > 5) return SK_ERR_BAD_ARGUMENT;
       if (value == 2 && !plan->w_rowmajor) return SK_ERR_UNAVAILABLE;
-      if (value == 5 && !plan->stream_scratch) return SK_ERR_UNAVAILABLE;
+      if (value == 5 && !plan->stream_scratch) {   // first request on a plan that did not get the scratch at creation
+        int cur = -1;
+        cudaGetDevice(&cur);
+        (void)cudaSetDevice(plan->device);
+        const int rc = sk::stream_setup(plan, 0);
+        if (cur >= 0 && cur != plan->device) (void)cudaSetDevice(cur);
+        if (rc != SK_OK) return rc;
+        if (!plan->stream_scratch) return SK_ERR_UNAVAILABLE;   // group size != 128 or K % 256 != 0
+      }
       if (value == 4 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       if (value == 3 && plan->G != 128) return SK_ERR_UNAVAILABLE;
       plan->opt_kernel = static_cast<int>(value);
@@ -966,7 +977,7 @@ int sk_w2a8_set_option(sk_w2a8_plan* plan, int key, int64_t value) {
       return SK_OK;
     case SK_OPT_STREAM_CTAS: {
       if (value < 0 || value > 65535) return SK_ERR_BAD_ARGUMENT;
-      if (!plan->stream_scratch) return SK_ERR_UNAVAILABLE;
+      if (plan->G != 128 || (plan->K % 256) != 0) return SK_ERR_UNAVAILABLE;
       int cur = -1;
       cudaGetDevice(&cur);
       (void)cudaSetDevice(plan->device);
