@@ -151,6 +151,17 @@ int sk_w2a8_gemm_rowscatter(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, in
 int sk_sum_row_blocks(const void* blocks, int n_blocks, int64_t block_stride, int64_t ld, int64_t rows, int64_t N,
                       void* out, int64_t ld_out, int out_dtype, sk_stream_t stream);
 
+/* Test aid.  Expands ONE tiled 128 x 128 weight block (4096 bytes, device) the way the general kernel's expander
+ * threads do -- 2-bit codes -> int8 (code - zero_point), stored in the 128-byte-swizzled K-major shared-memory
+ * layout -- and, next to it, lets the TMA load the same block given pre-expanded (int8 [128 rows][128 codes],
+ * row-major, device) through a tensor map with 128-byte swizzle.  Both 16 KiB shared-memory images are copied out
+ * (image_expander, image_tma) and *mismatches (zero it first) receives the number of bytes that differ; *device_status
+ * (zero it first) is set if the bounded wait for the TMA expired.  Follows the staging check of the reference's
+ * test_tma.cu (slimkernels/cute/gemm/test_tma.cu), which prints what a TMA load left in shared memory. */
+int sk_w2a8_debug_expander_image(const uint8_t* w_tiled_block, int zero_point, const int8_t* expanded_rowmajor,
+                                 uint8_t* image_expander, uint8_t* image_tma, int* mismatches, int* device_status,
+                                 sk_stream_t stream);
+
 /* Same contraction, but stores the exact per-group integer partial sums
  * partials[g, m, n] (int32, [K/G, M, N] contiguous) instead of the scaled output. */
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,

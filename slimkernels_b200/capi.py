@@ -46,6 +46,7 @@ SIGNATURES = {
     "sk_w2a8_gemm_debug_partials": (_int, [_vp, _i64, _vp, _i64, _vp, _vp]),
     "sk_quantize_activation_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "sk_silu_mul_quantize_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "sk_w2a8_debug_expander_image": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "sk_sum_row_blocks": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _vp, _i64, _int, _vp]),
     "sk_w2a8_quantize_weight": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "sk_w2a8_mlp_workspace_bytes": (_i64, [_vp, _vp, _i64]),

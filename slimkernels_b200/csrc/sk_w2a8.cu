@@ -529,6 +529,67 @@ __global__ void tile_scales_kernel(const __half* __restrict__ w_scale, __half* _
   }
 }
 
+
+// Test aid: the expander's shared-memory image of one 128 x 128 weight block next to the image the TMA writes for the
+// same int8 values.  One CTA: (a) copies a 4 KiB tiled block into shared memory and expands it exactly as the general
+// kernel's expander threads do (expand16, one row per thread, 16-byte stores into the 128-byte-swizzled K-major
+// layout); (b) loads the pre-expanded row-major int8 block through a tensor map with CU_TENSOR_MAP_SWIZZLE_128B -- the
+// layout the MMA's shared-memory descriptor expects of both operands; (c) writes both 16 KiB images out and counts
+// the bytes that differ.  The wait for the TMA is bounded.
+__global__ void __launch_bounds__(128)
+expander_image_kernel(const __grid_constant__ CUtensorMap tmap_expanded, const uint8_t* __restrict__ w_tiled_block,
+                      int zero_point, uint8_t* __restrict__ image_expander, uint8_t* __restrict__ image_tma,
+                      int* __restrict__ mismatches, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* wp = smem;                        // [4096] tiled 2-bit block
+  uint8_t* wx = smem + 4096;                 // [16384] expander image (1024-aligned: 4096 is)
+  uint8_t* wt = smem + 4096 + kWxBytes;      // [16384] TMA image
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  const uint32_t bar_a = smem_u32(&bar);
+  const int row = threadIdx.x;
+  if (threadIdx.x == 0) {
+    mbar_init(bar_a, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  for (int i = threadIdx.x; i < kWpBytes / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(wp)[i] = reinterpret_cast<const uint4*>(w_tiled_block)[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(bar_a, kWxBytes);
+    tma_load_2d(smem_u32(wt), &tmap_expanded, 0, 0, bar_a);
+  }
+  // (a) as the expander threads of w2a8_umma_kernel, one row per thread
+  const uint32_t lut = (static_cast<uint32_t>(0 - zero_point) & 0xffu) | ((static_cast<uint32_t>(1 - zero_point) & 0xffu) << 8) |
+                       ((static_cast<uint32_t>(2 - zero_point) & 0xffu) << 16) | ((static_cast<uint32_t>(3 - zero_point) & 0xffu) << 24);
+  const uint32_t src = smem_u32(wp) + row * 16;
+  const uint4 q0 = ld_shared_v4(src);
+  const uint4 q1 = ld_shared_v4(src + 2048);
+  const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+  const uint32_t dst = smem_u32(wx) + row * 128 + ((row & 7) << 4);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) st_shared_v4(dst ^ (c << 4), expand16(words[c], lut));
+  // (b) the TMA image
+  const WaitCtx ctx{&abort_flag, status, 200000000ll};
+  const bool ok = wait_bounded(bar_a, 0, ctx, kStExpanderFull);
+  __syncthreads();
+  if (!ok) return;
+  // (c)
+  int bad = 0;
+  for (int i = threadIdx.x; i < kWxBytes / 16; i += blockDim.x) {
+    const uint4 a = reinterpret_cast<const uint4*>(wx)[i], b = reinterpret_cast<const uint4*>(wt)[i];
+    reinterpret_cast<uint4*>(image_expander)[i] = a;
+    reinterpret_cast<uint4*>(image_tma)[i] = b;
+    const uint32_t x[4] = {a.x ^ b.x, a.y ^ b.y, a.z ^ b.z, a.w ^ b.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      for (int k = 0; k < 4; ++k) bad += ((x[j] >> (8 * k)) & 0xffu) ? 1 : 0;
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
 // partials[g] holds the running sum of its accumulator buffer; turn it into the group's own partial sum.
 __global__ void diff_partials_kernel(int32_t* __restrict__ partials, int groups, long long mn, int acc_bufs) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < mn;
@@ -1339,6 +1400,43 @@ int sk_w2a8_mlp_forward_static(sk_w2a8_plan* gate_up, sk_w2a8_plan* down, int64_
   rc = mlp_run(gate_up, down, M, x_f16, ld_x, out, ld_out, static_cast<char*>(scratch), stream);
   if (cur != dev) (void)cudaSetDevice(cur);
   return rc;
+}
+
+int sk_w2a8_debug_expander_image(const uint8_t* w_tiled_block, int zero_point, const int8_t* expanded_rowmajor,
+                                 uint8_t* image_expander, uint8_t* image_tma, int* mismatches, int* device_status,
+                                 sk_stream_t stream) {
+  if (!w_tiled_block || !expanded_rowmajor || !image_expander || !image_tma || !mismatches || !device_status)
+    return SK_ERR_NULL_POINTER;
+  if (zero_point < 0 || zero_point > 3) return SK_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(w_tiled_block) & 15) || (reinterpret_cast<uintptr_t>(expanded_rowmajor) & 15) ||
+      (reinterpret_cast<uintptr_t>(image_expander) & 15) || (reinterpret_cast<uintptr_t>(image_tma) & 15))
+    return SK_ERR_BAD_ALIGNMENT;
+  sk::EncodeTiledFn enc = sk::get_encode_fn();
+  if (!enc) return SK_ERR_CUDA;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {128, 128};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {128u, 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(expanded_rowmajor), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return SK_ERR_CUDA;
+  const int dyn = 4096 + 2 * sk::kWxBytes + 1024;
+  static int configured[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SK_ERR_CUDA;
+  if (dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(sk::expander_image_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return SK_ERR_CUDA;
+    }
+    configured[dev] = 1;
+  }
+  sk::expander_image_kernel<<<1, 128, dyn, static_cast<cudaStream_t>(stream)>>>(map, w_tiled_block, zero_point, image_expander,
+                                                                          image_tma, mismatches, device_status);
+  if (cudaGetLastError() != cudaSuccess) return SK_ERR_CUDA;
+  return SK_OK;
 }
 
 int sk_sum_row_blocks(const void* blocks, int n_blocks, int64_t block_stride, int64_t ld, int64_t rows, int64_t N,

@@ -269,6 +269,42 @@ def test_row_scatter_deals_token_rows_to_their_destinations(ld_extra):
                                        ld, dp.stream()) == capi.SK_ERR_UNAVAILABLE      # 128-token tile, 64 rows each
 
 
+@pytest.mark.parametrize("zp", [0, 1, 2, 3])
+def test_expander_shared_memory_image_matches_tma_of_pre_expanded_weights(zp):
+    """One 128 x 128 block: what the expander threads leave in shared memory (2-bit -> int8, swizzled K-major) against
+    what the TMA leaves there for the same values given as int8 -- byte for byte -- and against the 128-byte swizzle
+    written out on the host."""
+    from slimkernels_b200 import format as F
+    rng = np.random.default_rng(40 + zp)
+    codes = rng.integers(0, 4, size=(128, 128), dtype=np.uint8)                 # [feature row, k]
+    packed = F.pack_matrix(codes)                                                # matrix_packer layout [128, 32]
+    dev = torch.device("cuda")
+    lib = capi.load()
+    d_packed = torch.from_numpy(packed).to(dev)
+    tiled = torch.empty(4096, dtype=torch.uint8, device=dev)                     # one tiled block
+    assert lib.sk_w2a8_tiled_bytes(128, 128) == 4096
+    assert lib.sk_w2a8_repack(d_packed.data_ptr(), 128, 128, tiled.data_ptr(), torch.cuda.current_stream().cuda_stream) == capi.SK_OK
+    expanded = (codes.astype(np.int16) - zp).astype(np.int8)
+    d_exp = torch.from_numpy(expanded).to(dev)
+    img_a = torch.zeros(16384, dtype=torch.uint8, device=dev)
+    img_b = torch.zeros(16384, dtype=torch.uint8, device=dev)
+    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    rc = lib.sk_w2a8_debug_expander_image(tiled.data_ptr(), zp, d_exp.data_ptr(), img_a.data_ptr(), img_b.data_ptr(),
+                                          flags.data_ptr(), flags.data_ptr() + 4, torch.cuda.current_stream().cuda_stream)
+    assert rc == capi.SK_OK
+    torch.cuda.synchronize()
+    mism, status = flags.cpu().tolist()
+    assert status == 0 and mism == 0
+    a = img_a.cpu().numpy().view(np.int8).reshape(128, 8, 16)
+    assert np.array_equal(a, img_b.cpu().numpy().view(np.int8).reshape(128, 8, 16))
+    # row r at r * 128 bytes, its 16-byte chunk c at chunk position c ^ (r & 7)
+    want = np.empty_like(a)
+    for r in range(128):
+        for c in range(8):
+            want[r, c ^ (r & 7)] = expanded[r, 16 * c:16 * c + 16]
+    assert np.array_equal(a, want)
+
+
 def test_checker_kernel_matches_oracle():
     prob = random_problem(19, 200, 512, 128, seed=5)
     _check(prob, force=dict(kernel=capi.KERNEL_CUDA_CORE))
