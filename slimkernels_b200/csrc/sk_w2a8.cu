@@ -235,6 +235,7 @@ struct LaunchChoice {
   int split_k;     // 1 / 2 / 4 / 8
   int persistent;  // 1: one resident set of CTAs walks all tiles
   int ctas;        // CTAs launched
+  int mix_tiles1 = 0, mix_split = 0;   // decode kernel 3, mixed launch (see w2a8_decode.cuh); split_k then reports mix_split
 };
 
 static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
@@ -275,6 +276,20 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   }
   if (c.split_k > groups) c.split_k = 1;
   if (c.token_tile > 64) c.split_k = 1;   // the cluster reduction buffer is sized for small token tiles
+  // Decode kernel, one token tile, more feature tiles than SMs (but fewer than CTA slots): with one CTA per tile a
+  // few SMs carry two whole tiles and everybody waits for them.  Mixed launch instead: one CTA per tile for as many
+  // tiles as there are SMs (rounded down to whole clusters of four), the tiles beyond that split 4 ways (or 2 ways,
+  // if there are too many for that) so that they spread over the second CTA slot of many SMs in small pieces.
+  if (c.kernel == 3 && !plan->opt_split_k && M <= c.token_tile && c.split_k == 1) {
+    const int slots = 2 * plan->sm_count;
+    const int tiles1 = (plan->sm_count / 4) * 4;
+    const int rest = plan->n_tiles - tiles1;
+    if (rest > 0 && plan->n_tiles < slots) {
+      if (tiles1 + 4 * rest <= slots && groups >= 16) { c.mix_tiles1 = tiles1; c.mix_split = 4; }
+      else if ((rest % 2) == 0 && tiles1 + 2 * rest <= slots && groups >= 8) { c.mix_tiles1 = tiles1; c.mix_split = 2; }
+      if (c.mix_split) c.split_k = c.mix_split;
+    }
+  }
   // With more tiles than the machine holds at once, one resident set of CTAs can walk the tiles instead (option
   // SK_OPT_PERSISTENT = 2): the pipeline of the next tile fills while the previous tile is written out through TMA
   // stores.  Measured on B200 it is not reliably faster than one CTA per tile (all CTAs then move in lock-step and
@@ -284,6 +299,7 @@ static LaunchChoice choose(const sk_w2a8_plan* plan, long long M) {
   c.persistent = (plan->opt_persistent == 2 && tiles > capacity) ? 1 : 0;
   if (c.split_k > 1 || (c.token_tile != 128 && c.token_tile != 256)) c.persistent = 0;
   c.ctas = static_cast<int>(c.persistent ? (tiles < capacity ? tiles : capacity) : tiles * c.split_k);
+  if (c.mix_split) c.ctas = c.mix_tiles1 + (plan->n_tiles - c.mix_tiles1) * c.mix_split;
   // Pairs of CTAs (cta_group::2) are an option (SK_OPT_KERNEL = 4), not the default: measured on B200 the pair
   // kernel runs at ~1400 TOP/s where one CTA per tile runs at ~2300.  Its MMAs themselves run at full rate (128.8
   // cycles per 256 x 256 x 32), but every hand-over between the two CTAs costs ~290 cycles (remote mbarrier arrival,
@@ -328,7 +344,7 @@ static int launch_umma(sk_w2a8_plan* plan, const CUtensorMap& map, const CUtenso
 
 template <int TOK, bool DUMP>
 static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmParams& prm, int m_tiles, int split_k,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int mixed_ctas = 0) {
   using L = DecodeTraits<TOK>;
   auto kern = w2a8_decode_kernel<TOK, DUMP>;
   static int configured_device_mask[64] = {0};
@@ -338,13 +354,19 @@ static int launch_decode(sk_w2a8_plan* plan, const CUtensorMap& map, const GemmP
     configured_device_mask[plan->device] = 1;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(plan->n_tiles, m_tiles, split_k);
+  cfg.gridDim = mixed_ctas > 0 ? dim3(mixed_ctas, 1, 1) : dim3(plan->n_tiles, m_tiles, split_k);
   cfg.blockDim = dim3(L::kThreads, 1, 1);
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int na = 0;
-  if (split_k > 1) {
+  if (mixed_ctas > 0) {            // clusters of four along x: four single-tile CTAs, or the shares of one or two tiles
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 4;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  } else if (split_k > 1) {
     attr[na].id = cudaLaunchAttributeClusterDimension;
     attr[na].val.clusterDim.x = 1;
     attr[na].val.clusterDim.y = 1;
@@ -500,9 +522,10 @@ static int resolve_launch(const sk_w2a8_plan* plan, long long M, bool debug_part
   LaunchChoice ch = choose(plan, M);
   if (debug_partials) {
     if (ch.kernel == 5) { ch.kernel = 3; ch.ctas = static_cast<int>(plan->n_tiles * ((M + ch.token_tile - 1) / ch.token_tile)); }
-    ch.split_k = 1; ch.persistent = 0;
+    ch.split_k = 1; ch.persistent = 0; ch.mix_tiles1 = ch.mix_split = 0;
   }
-  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.split_k, ch.kernel)) {
+  // (mixed launch: the CTAs with a tile of their own run the whole depth)
+  if (ch.kernel != 2 && !running_sum_fits(plan, ch.token_tile, ch.mix_split ? 1 : ch.split_k, ch.kernel)) {
     if (ch.token_tile >= 192 && !plan->opt_token_tile && running_sum_fits(plan, 128, 1, 1)) {
       ch.token_tile = 128;
       ch.persistent = 0;
@@ -740,6 +763,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       prm.out_bf16 = plan->out_dtype == SK_OUT_BF16;
       prm.wait_limit = plan->opt_wait_limit > 0 ? plan->opt_wait_limit : kWaitLimitCycles;
       prm.fault_skip_kb = plan->opt_skip_copy - 1;
+      prm.mix_tiles1 = partials ? 0 : ch.mix_tiles1;
+      prm.mix_split = partials ? 0 : ch.mix_split;
       prm.stream_scratch = plan->stream_scratch;
       prm.stream_counters = plan->stream_counters;
       prm.stream_slots = plan->stream_slots;
@@ -797,8 +822,8 @@ static int run_gemm(sk_w2a8_plan* plan, long long M, const int8_t* x_q, long lon
       else if (ch.kernel == 5)
         rc = dispatch_stream(plan, ch.token_tile, map, prm, stream);
       else if (ch.kernel == 3)
-        rc = ch.token_tile == 16 ? launch_decode<16, false>(plan, map, prm, m_tiles, ch.split_k, stream)
-                                 : launch_decode<32, false>(plan, map, prm, m_tiles, ch.split_k, stream);
+        rc = ch.token_tile == 16 ? launch_decode<16, false>(plan, map, prm, m_tiles, ch.split_k, stream, ch.mix_split ? ch.ctas : 0)
+                                 : launch_decode<32, false>(plan, map, prm, m_tiles, ch.split_k, stream, ch.mix_split ? ch.ctas : 0);
       else if (ch.kernel == 4) rc = launch_pair<false>(plan, map, out_map, extra_maps, prm, m_tiles, stream);
       else rc = dispatch_umma<false>(plan, ch.token_tile, map, out_map, extra_maps, prm, m_tiles, ch.split_k, persist ? ch.ctas : 0, stream);
     }
@@ -1134,13 +1159,20 @@ int sk_w2a8_launch_floor_probe(sk_w2a8_plan* plan, int64_t M, sk_stream_t stream
   if (e == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
     const int m_tiles = static_cast<int>((M + ch.token_tile - 1) / ch.token_tile);
-    cfg.gridDim = ch.kernel == 5 ? dim3(plan->stream_ctas, 1, 1) : dim3(plan->n_tiles, m_tiles, ch.split_k);
+    cfg.gridDim = ch.kernel == 5 ? dim3(plan->stream_ctas, 1, 1)
+                  : ch.mix_split ? dim3(ch.ctas, 1, 1) : dim3(plan->n_tiles, m_tiles, ch.split_k);
     cfg.blockDim = dim3(sk::DecodeTraits<16>::kThreads, 1, 1);
     cfg.dynamicSmemBytes = dyn - 1024;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
     int na = 0;
-    if (ch.split_k > 1) {
+    if (ch.kernel == 3 && ch.mix_split) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 4;
+      attr[na].val.clusterDim.y = 1;
+      attr[na].val.clusterDim.z = 1;
+      ++na;
+    } else if (ch.kernel == 3 && ch.split_k > 1) {
       attr[na].id = cudaLaunchAttributeClusterDimension;
       attr[na].val.clusterDim.x = 1;
       attr[na].val.clusterDim.y = 1;

@@ -112,11 +112,22 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x;
-  const int n0 = n_tile * kTileN;
+  // Which tile and which share of its K range.  Plain launch: grid (feature tiles, token tiles, splits), one cluster
+  // per tile.  Mixed launch (p.mix_split > 0; one token tile; more tiles than SMs): a 1-D grid in clusters of four --
+  // the first p.mix_tiles1 tiles get one CTA each (four unrelated tiles per cluster, no reduction), every further
+  // tile is split 4 ways over one cluster or 2 ways over half a cluster, so that the tiles beyond one per SM are
+  // dealt out in small pieces instead of doubling the load of a few SMs.
+  int n_tile = blockIdx.x, split = blockIdx.z, num_splits = gridDim.z;
+  int grp_base = 0;          // cluster rank of split 0 of this tile
   const int m0 = blockIdx.y * TOK;
-  const int split = blockIdx.z;
-  const int num_splits = gridDim.z;
+  if (p.mix_split > 0) {
+    const int cluster = blockIdx.x >> 2, rank = blockIdx.x & 3;
+    const int c1 = p.mix_tiles1 >> 2;
+    if (cluster < c1) { n_tile = blockIdx.x; split = 0; num_splits = 1; }
+    else if (p.mix_split == 4) { n_tile = p.mix_tiles1 + (cluster - c1); split = rank; num_splits = 4; }
+    else { n_tile = p.mix_tiles1 + 2 * (cluster - c1) + (rank >> 1); split = rank & 1; num_splits = 2; grp_base = rank & 2; }
+  }
+  const int n0 = n_tile * kTileN;
 
   // K range of this CTA in K blocks (one scale group each)
   const int per_split = (p.groups + num_splits - 1) / num_splits;
@@ -453,13 +464,13 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
         // split-K: push this CTA's partial sums into the CTAs that own the token rows (row j belongs to cluster
         // rank j mod num_splits; slot (j div num_splits) * num_splits + this rank of its buffer).  Remote stores
         // do not stall the way remote loads do, and after the cluster barrier every CTA only reads its own memory.
-        const uint32_t my_rank = cluster_ctarank();
-        const int sh = num_splits == 2 ? 1 : num_splits == 4 ? 2 : 3;   // cluster sizes are 2, 4 or 8
+        const uint32_t my_rank = static_cast<uint32_t>(split);
+        const int sh = num_splits == 2 ? 1 : num_splits == 4 ? 2 : 3;   // a tile is shared by 2, 4 or 8 CTAs
         const uint32_t red_base = smem_base + T::kOffRed + row * 4;
 #pragma unroll
         for (int t = 0; t < TOK; ++t) {
           const uint32_t slot = (static_cast<uint32_t>(t >> sh) << sh) + my_rank;
-          st_dsmem_f32(map_to_cta(red_base + slot * (kTileN * 4), static_cast<uint32_t>(t & (num_splits - 1))), acc[t]);
+          st_dsmem_f32(map_to_cta(red_base + slot * (kTileN * 4), static_cast<uint32_t>(grp_base + (t & (num_splits - 1)))), acc[t]);
         }
       }
     }
@@ -475,7 +486,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       // k * num_splits + r of the buffer holds rank r's partial sum of row my_rank + k * num_splits.
       const float kScaleDown = 5.62949953421312e14f;
       grid_dep_wait();
-      const int my_rank = static_cast<int>(cluster_ctarank());
+      const int my_rank = split;
       const int rows = TOK / num_splits;
       constexpr int kMaxIter = (TOK / 2 * kTileN + T::kThreads - 1) / T::kThreads;
       float xs[kMaxIter];     // the token scales of this thread's outputs, fetched before the barrier

@@ -108,6 +108,8 @@ struct GemmParams {
   long long wait_limit;       // SM cycles after which a wait inside the kernel gives up (kWaitLimitCycles by default)
   int fault_skip_kb;          // failure-path test hook: the producer leaves out the copies of this K block of its
                               // range (-1: off), so that the waits for them run into the limit
+  int mix_tiles1;             // decode kernel with clusters, mixed launch: tiles that get a CTA of their own (multiple of 4)
+  int mix_split;              // ... and how the further tiles are split (4 or 2); 0: plain launch
   // balanced-split decode kernel (w2a8_stream.cuh): partial sums of tiles shared between CTAs
   float* stream_scratch;      // [n_tiles][stream_slots][token tile][128] fp32
   int* stream_counters;       // [n_tiles][4]: contributions received per (tile, epilogue warp); zero between launches

@@ -160,6 +160,36 @@ def test_balanced_split_is_the_default_for_large_decode_problems():
         assert np.abs(y[:, cols] - y_ref).max() <= TOL
 
 
+@pytest.mark.parametrize("extra,K,M", [(2, 2048, 16), (9, 2048, 13), (36, 4096, 29), (44, 1024, 16), (60, 2048, 32), (41, 2048, 16)])
+def test_decode_kernel_mixed_launch_when_there_are_more_tiles_than_sms(extra, K, M):
+    """More feature tiles than SMs (but fewer than CTA slots): one CTA per tile for one tile per SM, the tiles beyond
+    that split 4 ways (few of them) or 2 ways (an even number of them) inside clusters of four."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    tiles1 = (sms // 4) * 4
+    n_tiles = tiles1 + extra
+    N = n_tiles * 128 - 5                     # ragged last tile
+    x_q, xs, wp, ws = random_problem(M, N, K, 128, seed=extra + K)
+    dp = DeviceProblem(x_q, xs, wp, ws)
+    q = dp.plan.query_launch(M)
+    slots = 2 * sms
+    if tiles1 + 4 * extra <= slots and K // 128 >= 16:
+        want = 4
+    elif extra % 2 == 0 and tiles1 + 2 * extra <= slots and K // 128 >= 8:
+        want = 2
+    else:
+        want = 1
+    assert q["kernel"] == capi.KERNEL_TCGEN05_DECODE and q["split_k"] == want
+    assert q["ctas"] == (tiles1 + extra * want if want > 1 else n_tiles)
+    y = dp.gemm()
+    cols = np.unique(np.concatenate([np.arange(0, N, 701), np.arange(tiles1 * 128 - 64, N)]))   # incl. every split tile
+    y_ref = O.w2a8_gemm_dequant_path(x_q, xs, wp[cols], ws[:, cols])
+    assert np.abs(to_np(y)[:, cols] - y_ref).max() <= TOL
+    assert torch.equal(dp.gemm(), y)
+    # against a plain launch (one CTA per tile)
+    y_plain = dp.force(kernel=capi.KERNEL_TCGEN05_DECODE, split_k=1).gemm()
+    assert np.abs(to_np(y) - to_np(y_plain)).max() <= 4e-3 * max(1.0, float(np.abs(y_ref).max()))
+
+
 def test_decode_kernel_is_the_default_for_small_batches():
     x_q, xs, wp, ws = random_problem(8, 512, 2048, 128, seed=3)
     dp = DeviceProblem(x_q, xs, wp, ws)
