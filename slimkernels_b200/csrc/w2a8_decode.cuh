@@ -78,8 +78,11 @@ struct DecodeTraits {
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;
   static constexpr int kTotal = kOffMisc + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;        // slack for 1024-byte alignment of the base
+  // (eight expander warps -- two groups taking the half stages in turn -- measure the same at 16 tokens and slower at
+  // 32, where the kernel then spills under the 64-register budget of two 512-thread CTAs per SM)
   static constexpr int kEpiWarps = 4, kExpWarps = 4;
-  static constexpr int kThreads = 384;                       // 4 epilogue + 4 expander + producer + 2 MMA warps, + 1 idle
+  static constexpr int kExpGroups = kExpWarps / 4;           // groups of four warps take the half stages in turn
+  static constexpr int kThreads = (kEpiWarps + kExpWarps + 4) * 32;   // + producer + 2 MMA warps + 1 idle
   static_assert(2 * (kDynamicBytes + 1024) <= 228 * 1024, "two CTAs per SM (1 KiB per CTA is reserved by the system)");
 };
 
@@ -166,7 +169,7 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
       w += static_cast<size_t>(n) * kWpBytes;
     }
     for (int i = 0; i < T::kSubRing; ++i) mbar_init(bar_sub_done + 8 * i, 1);
-    for (int i = 0; i < T::kASubs; ++i) mbar_init(bar_ex_full + 8 * i, T::kExpWarps);
+    for (int i = 0; i < T::kASubs; ++i) mbar_init(bar_ex_full + 8 * i, 4);
     for (int i = 0; i < T::kAccSets; ++i) mbar_init(bar_acc_empty + 8 * i, T::kEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
@@ -286,22 +289,24 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
     const uint32_t lut = (static_cast<uint32_t>(0 - zp) & 0xffu) | ((static_cast<uint32_t>(1 - zp) & 0xffu) << 8) |
                          ((static_cast<uint32_t>(2 - zp) & 0xffu) << 16) | ((static_cast<uint32_t>(3 - zp) & 0xffu) << 24);
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + T::kACol0;
-    int stage = 0, a = 0;
-    uint32_t lph = 0;
+    const int group = (warp - kExpWarp0) >> 2;
     bool ok = true;
     grid_dep_wait();   // a stage is complete only with its activations: do not poll next to the running kernel
-    for (int i = 0; i < nkb && ok; i += 2) {
-      if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(6, (i >> 1) * 8 + 0);
+    const int num_subs = (nkb + 1) >> 1;
+    for (int u = group; u < num_subs && ok; u += T::kExpGroups) {
+      const int i = 2 * u;
+      const int q = u >> 1;
+      const int stage = q % S;
+      const int a = u % T::kASubs;
       // The loads below must not be issued before the waits have been seen to succeed: a load that does not depend
       // on the poll's predicate can be served before the barrier state is sampled and return stale bytes.
-      if ((i & 3) == 0) ok = wait_bounded(bar_ld_full + 8 * stage, lph, ctx, kStExpanderFull);
-      if (ok && (i >> 1) >= T::kASubs) {   // the buffer is free once the MMAs that read its previous contents are complete
-        const int u = (i >> 1) - T::kASubs;
-        ok = wait_bounded(bar_sub_done + 8 * (u % T::kSubRing), (u / T::kSubRing) & 1, ctx, kStExpanderEmpty);
+      ok = wait_bounded(bar_ld_full + 8 * stage, (q / S) & 1, ctx, kStExpanderFull);
+      if (ok && u >= T::kASubs) {   // the buffer is free once the MMAs that read its previous contents are complete
+        const int v = u - T::kASubs;
+        ok = wait_bounded(bar_sub_done + 8 * (v % T::kSubRing), (v / T::kSubRing) & 1, ctx, kStExpanderEmpty);
       }
       if (!ok) break;
       tcgen05_fence_after_sync();
-      if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(6, (i >> 1) * 8 + 1);
       const int n = min(2, nkb - i);
       for (int j = 0; j < n; ++j) {
         const uint32_t wp = smem_base + stage * T::kStageBytes + ((i & 3) + j) * kWpBytes + row * 16;
@@ -315,16 +320,12 @@ w2a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams 
           a_row[4 * c] = o.x; a_row[4 * c + 1] = o.y; a_row[4 * c + 2] = o.z; a_row[4 * c + 3] = o.w;
         }
         tmem_st_32x32(t_row + a * 64 + j * 32, a_row);
-        if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(6, (i >> 1) * 8 + 2 + j);
       }
       tmem_st_wait();
-      if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(6, (i >> 1) * 8 + 4);
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ex_full + 8 * a);
-      if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, i >> 1);
-      if ((i & 3) == 2 && ++stage == S) { stage = 0; lph ^= 1; }
-      if (++a == T::kASubs) a = 0;
+      if (threadIdx.x == kExpWarp0 * 32) SK_TRACE_EVENT(1, u);
     }
   } else if (warp < T::kEpiWarps) {
     // ============================================================ epilogue: TMEM lane = output feature
