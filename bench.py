@@ -800,14 +800,25 @@ def run_ours(args):
     if not args.no_sweeps or world > 1:
         few = max(3, min(args.steps, 10))
         extra = {}
-        extra["down_proj"] = strip(measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, fused, few, peaks))
+        def guarded(name, fn):
+            # an extra workload that raises (the same way on every rank: shapes, memory) is reported, not fatal: the
+            # headline measurement above stands by itself
+            try:
+                return fn()
+            except Exception as exc:            # noqa: BLE001
+                return {"error": f"{name}: {type(exc).__name__}: {exc}"[:400]}
+
+        extra["down_proj"] = guarded("down_proj", lambda: strip(
+            measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, fused, few, peaks)))
         if world > 1:
-            extra["gate_up_other_exchange"] = strip(measure_workload(WORKLOAD, 0, args, dev, world, rank, not fused, few, peaks))
-            extra["down_proj_other_exchange"] = strip(measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, not fused, few, peaks))
-            ks = measure_k_sharded(WORKLOAD_DOWN, 2, args, dev, world, rank, few)
+            extra["gate_up_other_exchange"] = guarded("gate_up_other_exchange", lambda: strip(
+                measure_workload(WORKLOAD, 0, args, dev, world, rank, not fused, few, peaks)))
+            extra["down_proj_other_exchange"] = guarded("down_proj_other_exchange", lambda: strip(
+                measure_workload(WORKLOAD_DOWN, 1, args, dev, world, rank, not fused, few, peaks)))
+            ks = guarded("down_proj_k_sharded", lambda: measure_k_sharded(WORKLOAD_DOWN, 2, args, dev, world, rank, few))
             k_sharded_ok = ks.pop("_ok", True)
             extra["down_proj_k_sharded"] = ks
-            tp = measure_tp_mlp(3, dev, world, rank, few)
+            tp = guarded("mlp_block_tensor_parallel", lambda: measure_tp_mlp(3, dev, world, rank, few))
             k_sharded_ok = k_sharded_ok and tp.get("fused_equals_nccl_bitwise", True) and tp.get("finite", True)
             extra["mlp_block_tensor_parallel"] = tp
         line["config3"] = extra
