@@ -70,9 +70,9 @@ typedef enum sk_option {
   SK_OPT_SPLIT_K = 3,     /* CTAs (one cluster) sharing the K range of one tile: 0 auto, 1, 2, 4, 8 */
   SK_OPT_TMA_STORE = 6,   /* general kernel, one CTA per tile: 0 auto (= 2), 1 vector stores by the epilogue threads, 2 one TMA
                              store per destination where alignment allows (16-byte base, pitch % 8 == 0, N % 8 == 0) */
-  SK_OPT_DEPENDENT_LAUNCH = 5, /* decode kernel: 0 auto (2 when the grid has more CTAs than the GPU has SMs, else 1),
-                             1 plain launch, 2 programmatic dependent launch: the kernel's set-up and first weight
-                             copies overlap the tail of the previous kernel in the stream */
+  SK_OPT_DEPENDENT_LAUNCH = 5, /* decode kernels: 0 auto (= 2), 1 plain launch, 2 programmatic dependent launch: the
+                             kernel's set-up and first weight copies overlap the tail of the previous kernel in the
+                             stream; it waits for that kernel before it reads activations or writes outputs */
   SK_OPT_PERSISTENT = 4,  /* 0 auto (= 1), 1 one CTA per tile, 2 one resident set of CTAs walks all tiles (token tiles
                              128 / 256 without split-K, when there are more tiles than the GPU holds at once) */
   SK_OPT_WAIT_LIMIT_CYCLES = 7, /* SM cycles after which a wait inside a kernel gives up and the kernel returns with a
