@@ -162,6 +162,12 @@ int sk_w2a8_debug_expander_image(const uint8_t* w_tiled_block, int zero_point, c
                                  uint8_t* image_expander, uint8_t* image_tma, int* mismatches, int* device_status,
                                  sk_stream_t stream);
 
+/* Test aid, host only (no device is touched): the cut of the balanced-split decode kernel.  With `units` half stages
+ * dealt to `ctas` CTAs, CTA `cta` owns [*range_begin, *range_end); *owner_of_unit is the CTA whose range holds `unit`.
+ * The kernel and the host size their slots with these two formulas; a test checks that they agree for every unit. */
+int sk_w2a8_debug_stream_cut(int64_t units, int ctas, int cta, int64_t unit, int64_t* range_begin, int64_t* range_end,
+                             int* owner_of_unit);
+
 /* Same contraction, but stores the exact per-group integer partial sums
  * partials[g, m, n] (int32, [K/G, M, N] contiguous) instead of the scaled output. */
 int sk_w2a8_gemm_debug_partials(sk_w2a8_plan* plan, int64_t M, const int8_t* x_q, int64_t ld_x,

@@ -47,6 +47,7 @@ SIGNATURES = {
     "sk_quantize_activation_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "sk_silu_mul_quantize_int8": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp]),
     "sk_w2a8_debug_expander_image": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "sk_w2a8_debug_stream_cut": (_int, [_i64, _int, _int, _i64, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_int)]),
     "sk_sum_row_blocks": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _vp, _i64, _int, _vp]),
     "sk_w2a8_quantize_weight": (_int, [_vp, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "sk_w2a8_mlp_workspace_bytes": (_i64, [_vp, _vp, _i64]),

@@ -1471,6 +1471,15 @@ int sk_w2a8_debug_expander_image(const uint8_t* w_tiled_block, int zero_point, c
   return SK_OK;
 }
 
+int sk_w2a8_debug_stream_cut(int64_t units, int ctas, int cta, int64_t unit, int64_t* range_begin, int64_t* range_end,
+                             int* owner_of_unit) {
+  if (units <= 0 || ctas <= 0 || ctas > units || cta < 0 || cta >= ctas || unit < 0 || unit >= units) return SK_ERR_BAD_ARGUMENT;
+  if (range_begin) *range_begin = sk::stream_range_begin(units, ctas, cta);
+  if (range_end) *range_end = sk::stream_range_begin(units, ctas, cta + 1);
+  if (owner_of_unit) *owner_of_unit = sk::stream_owner(units, ctas, unit);
+  return SK_OK;
+}
+
 int sk_sum_row_blocks(const void* blocks, int n_blocks, int64_t block_stride, int64_t ld, int64_t rows, int64_t N,
                       void* out, int64_t ld_out, int out_dtype, sk_stream_t stream) {
   if (!blocks || !out) return SK_ERR_NULL_POINTER;

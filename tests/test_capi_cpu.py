@@ -4,6 +4,7 @@ import ctypes
 import os
 import re
 
+import numpy as np
 import pytest
 
 from conftest import ROOT
@@ -75,3 +76,29 @@ def test_product_path_fails_loudly_without_gpu(built_libs):
     ws = torch.ones(1, 128, dtype=torch.float16)
     with pytest.raises(RuntimeError):
         ops.w2a8_gemm(x_q, xs, wp, ws)
+
+
+def test_balanced_split_cut_is_a_partition_and_owner_inverts_it():
+    """Host arithmetic of the balanced-split decode kernel: the CTA ranges tile [0, units) without gaps, differ by at
+    most one half stage, and stream_owner names the range that holds a half stage (the kernel derives the slots of a
+    shared tile from it)."""
+    import ctypes
+    from slimkernels_b200 import capi
+    lib = capi.load()
+    rng = np.random.default_rng(0)
+    cases = [(1, 1), (16, 16), (1536, 296), (5504, 296), (5504, 148), (14336, 296), (7, 3), (1000, 999)]
+    cases += [(int(u), int(c)) for u in rng.integers(1, 5000, size=20) for c in rng.integers(1, 400, size=2) if c <= u]
+    for units, ctas in cases:
+        b, e, o = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int()
+        prev_end, sizes = 0, []
+        for c in range(ctas):
+            assert lib.sk_w2a8_debug_stream_cut(units, ctas, c, 0, ctypes.byref(b), ctypes.byref(e), None) == capi.SK_OK
+            assert b.value == prev_end and e.value >= b.value
+            sizes.append(e.value - b.value)
+            prev_end = e.value
+            for x in {b.value, e.value - 1, (b.value + e.value) // 2}:
+                if b.value <= x < e.value:
+                    assert lib.sk_w2a8_debug_stream_cut(units, ctas, 0, x, None, None, ctypes.byref(o)) == capi.SK_OK
+                    assert o.value == c, (units, ctas, c, x, o.value)
+        assert prev_end == units and max(sizes) - min(sizes) <= 1 and min(sizes) >= 1
+    assert lib.sk_w2a8_debug_stream_cut(4, 5, 0, 0, None, None, None) == capi.SK_ERR_BAD_ARGUMENT
