@@ -52,7 +52,7 @@ __device__ __forceinline__ uint32_t quantize_one_fast(float x, float s, float r)
   float t = fminf(fmaxf(x * r, -127.f), 127.f);
   float big = t + kMagic;
   const float q = big - kMagic;
-  if (fabsf(fabsf(t - q) - 0.5f) < 1e-3f) {                      // rare: decided by the exact quotient
+  if (fabsf(t - q) > 0.499f) {                                   // (|t - q| <= 0.5) rare: decided by the exact quotient
     t = fminf(fmaxf(x / s, -127.f), 127.f);
     big = t + kMagic;
   }
